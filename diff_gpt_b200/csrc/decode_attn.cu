@@ -1,0 +1,269 @@
+// Decode attention (one query per row) over paged K/V, split along the keys.
+//
+// One warp per (row, head, split).  A K or V vector of D elements is read as
+// D*sizeof(T)/16 sixteen-byte loads, one per lane, so a warp covers 32/LPT tokens
+// per load instruction (LPT = lanes per token) and every byte of the cache is
+// fetched with 128-bit coalesced accesses.  Each lane group keeps its own online
+// softmax state; the groups are merged with shuffles at the end, so the inner
+// loop has no cross-group dependency.  HBM-bound by design: the algorithmic
+// traffic is 2 * D * sizeof(T) bytes per (row, head, key).
+#include "common.cuh"
+
+namespace dgpt {
+
+template <typename T, int D>
+struct DecodeCfg {
+  static constexpr int VEC = Io<T>::kVec16;
+  static constexpr int LPT = D / VEC;    // lanes per token
+  static constexpr int TPW = 32 / LPT;   // tokens per warp-wide load
+  static_assert(D % VEC == 0 && LPT >= 1 && LPT <= 32 && (LPT & (LPT - 1)) == 0, "unsupported head_dim");
+};
+
+struct MergeState {
+  float m, l;
+};
+
+// merge (m,l,acc) with (m2,l2,acc2): log2-domain running max
+template <int VEC>
+__device__ __forceinline__ void merge_partial(float& m, float& l, float* acc, float m2, float l2, const float* acc2) {
+  const float mn = fmaxf(m, m2);
+  const float a = (m == -INFINITY) ? 0.f : exp2f(m - mn);
+  const float b = (m2 == -INFINITY) ? 0.f : exp2f(m2 - mn);
+  l = l * a + l2 * b;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) acc[i] = acc[i] * a + acc2[i] * b;
+  m = mn;
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(128)
+decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const int* __restrict__ len0,
+                   const int* __restrict__ start1, const int* __restrict__ len1, const int* __restrict__ step_ptr,
+                   const float* __restrict__ prefix_o, const float* __restrict__ prefix_lse,
+                   const T* __restrict__ gate, long long gate_stride, T* __restrict__ y, long long y_stride,
+                   float* __restrict__ ws_ml, float* __restrict__ ws_o, int n_splits, int R, int H,
+                   float scale_log2) {
+  using Cfg = DecodeCfg<T, D>;
+  constexpr int VEC = Cfg::VEC, LPT = Cfg::LPT, TPW = Cfg::TPW;
+  const long long rh = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (rh >= (long long)R * H) return;
+  const int r = (int)(rh / H), h = (int)(rh - (long long)r * H);
+  const int lane = threadIdx.x & 31;
+  const int g = lane / LPT, e = lane - g * LPT;
+  const int split = blockIdx.y;
+  const int step = step_ptr ? *step_ptr : 0;
+  const bool have_prefix = prefix_lse != nullptr;
+  const int n0 = have_prefix ? 0 : len0[r];
+  const int s1 = start1[r];
+  const int n = n0 + len1[r] + step;
+  int chunk = (n + n_splits - 1) / n_splits;
+  chunk = (chunk + 2 * TPW - 1) / (2 * TPW) * (2 * TPW);
+  const int begin = split * chunk;
+  const int end = min(n, begin + chunk);
+
+  float qf[VEC];
+  ld16<T>(q + (long long)r * q_stride + (long long)h * D + e * VEC, qf);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) qf[i] *= scale_log2;
+
+  float m = -INFINITY, l = 0.f, acc[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+
+  const T* kbase = static_cast<const T*>(kv.k);
+  const T* vbase = static_cast<const T*>(kv.v);
+  for (int i0 = begin; i0 < end; i0 += 2 * TPW) {  // warp-uniform trip count
+    float kf[2][VEC], vf[2][VEC];
+    bool ok[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int i = i0 + u * TPW + g;
+      ok[u] = i < end;
+      if (ok[u]) {
+        const int slot = i < n0 ? i : s1 + (i - n0);
+        const long long off = kv_offset(kv, r, h, slot, D) + e * VEC;
+        ld16<T>(kbase + off, kf[u]);
+        ld16<T>(vbase + off, vf[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      float s = 0.f;
+      if (ok[u]) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) s += qf[i] * kf[u][i];
+      }
+#pragma unroll
+      for (int o = LPT >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (ok[u]) {
+        const float mn = fmaxf(m, s);
+        const float resc = exp2f(m - mn);  // m = -inf -> 0
+        const float p = exp2f(s - mn);
+        l = l * resc + p;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = acc[i] * resc + p * vf[u][i];
+        m = mn;
+      }
+    }
+  }
+  // merge the TPW lane groups (butterfly: every lane ends with the full state)
+#pragma unroll
+  for (int o = LPT; o < 32; o <<= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+    const float l2 = __shfl_xor_sync(0xffffffffu, l, o);
+    float a2[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) a2[i] = __shfl_xor_sync(0xffffffffu, acc[i], o);
+    merge_partial<VEC>(m, l, acc, m2, l2, a2);
+  }
+  if (g != 0) return;
+
+  if (n_splits > 1) {
+    const long long slot = (long long)split * R * H + rh;
+    if (e == 0) {
+      ws_ml[2 * slot] = m;
+      ws_ml[2 * slot + 1] = l;
+    }
+    float* dst = ws_o + slot * D + e * VEC;
+#pragma unroll
+    for (int i = 0; i < VEC; i += 4)
+      *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+    return;
+  }
+  if (have_prefix) {
+    const float mp = prefix_lse[rh] * kLog2e;  // normalised partial: l = 1
+    float po[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; i += 4) {
+      const float4 t = *reinterpret_cast<const float4*>(prefix_o + rh * D + e * VEC + i);
+      po[i] = t.x; po[i + 1] = t.y; po[i + 2] = t.z; po[i + 3] = t.w;
+    }
+    merge_partial<VEC>(m, l, acc, mp, 1.f, po);
+  }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  float out[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) out[i] = Io<T>::round(acc[i] * inv);
+  if (gate) {
+    float gf[VEC];
+    ld16<T>(gate + (long long)r * gate_stride + (long long)h * D + e * VEC, gf);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) out[i] *= Io<T>::round(1.f / (1.f + __expf(-gf[i])));
+  }
+  T* dst = y + (long long)r * y_stride + (long long)h * D + e * VEC;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) Io<T>::st(dst + i, out[i]);
+}
+
+// Second pass of the split path: one thread per (row, head, d).
+template <typename T>
+__global__ void decode_combine_kernel(const float* __restrict__ ws_ml, const float* __restrict__ ws_o, int n_splits,
+                                      const float* __restrict__ prefix_o, const float* __restrict__ prefix_lse,
+                                      const T* __restrict__ gate, long long gate_stride, T* __restrict__ y,
+                                      long long y_stride, int R, int H, int D) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long RH = (long long)R * H;
+  if (idx >= RH * D) return;
+  const long long rh = idx / D;
+  const int d = (int)(idx - rh * D);
+  const int r = (int)(rh / H), h = (int)(rh - (long long)r * H);
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, ws_ml[2 * (s * RH + rh)]);
+  const float mp = prefix_lse ? prefix_lse[rh] * kLog2e : -INFINITY;
+  m = fmaxf(m, mp);
+  float l = 0.f, acc = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = ws_ml[2 * (s * RH + rh)];
+    const float w = ms == -INFINITY ? 0.f : exp2f(ms - m);
+    l += ws_ml[2 * (s * RH + rh) + 1] * w;
+    acc += ws_o[(s * RH + rh) * D + d] * w;
+  }
+  if (prefix_lse) {
+    const float w = mp == -INFINITY ? 0.f : exp2f(mp - m);
+    l += w;
+    acc += prefix_o[rh * D + d] * w;
+  }
+  float out = Io<T>::round(l > 0.f ? acc / l : 0.f);
+  if (gate) out *= Io<T>::round(1.f / (1.f + __expf(-Io<T>::ld(gate + (long long)r * gate_stride + (long long)h * D + d))));
+  Io<T>::st(y + (long long)r * y_stride + (long long)h * D + d, out);
+}
+
+template <typename T, int D>
+static int decode_launch(const void* q, long long q_stride, const KvView& kv, const int* len0, const int* start1,
+                         const int* len1, const int* step_ptr, const float* prefix_o, const float* prefix_lse,
+                         const void* gate, long long gate_stride, void* y, long long y_stride, float* ws,
+                         int n_splits, int R, int H, cudaStream_t st) {
+  const long long RH = (long long)R * H;
+  float* ws_ml = ws;
+  float* ws_o = ws ? ws + 2 * RH * n_splits : nullptr;
+  const float scale_log2 = kLog2e / sqrtf((float)D);
+  dim3 grid((unsigned)((RH + 3) / 4), (unsigned)n_splits);
+  decode_attn_kernel<T, D><<<grid, 128, 0, st>>>(static_cast<const T*>(q), q_stride, kv, len0, start1, len1, step_ptr,
+                                                 prefix_o, prefix_lse, static_cast<const T*>(gate), gate_stride,
+                                                 static_cast<T*>(y), y_stride, ws_ml, ws_o, n_splits, R, H, scale_log2);
+  if (int e = launch_status("decode_attn")) return e;
+  if (n_splits > 1) {
+    const long long n = RH * D;
+    decode_combine_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+        ws_ml, ws_o, n_splits, prefix_o, prefix_lse, static_cast<const T*>(gate), gate_stride, static_cast<T*>(y),
+        y_stride, R, H, D);
+    return launch_status("decode_combine");
+  }
+  return DGPT_OK;
+}
+
+}  // namespace dgpt
+
+using namespace dgpt;
+
+extern "C" size_t dgpt_decode_attn_workspace_bytes(int32_t R, int32_t H, int32_t D, int32_t n_splits) {
+  if (n_splits <= 1) return 0;
+  return (size_t)R * H * n_splits * (size_t)(D + 2) * sizeof(float);
+}
+
+extern "C" int dgpt_decode_attn(const void* q, int64_t q_row_stride, const dgpt_kv_layout* kv, const int32_t* len0,
+                                const int32_t* start1, const int32_t* len1, const int32_t* step_ptr,
+                                const float* prefix_o, const float* prefix_lse, const void* gate,
+                                int64_t gate_row_stride, void* y, int64_t y_row_stride, void* workspace,
+                                size_t workspace_bytes, int32_t n_splits, int32_t R, int32_t H, int32_t D,
+                                int32_t dtype, void* stream) {
+  DGPT_REQUIRE(q && y && len0 && start1 && len1, "decode_attn: NULL pointer");
+  DGPT_REQUIRE(R >= 0 && H > 0 && n_splits >= 1 && n_splits <= 65535, "decode_attn: bad sizes");
+  DGPT_REQUIRE((prefix_o == nullptr) == (prefix_lse == nullptr), "decode_attn: prefix_o and prefix_lse go together");
+  DGPT_REQUIRE(q_row_stride % 8 == 0 && y_row_stride % 8 == 0 && gate_row_stride % 8 == 0,
+               "decode_attn: row strides must be multiples of 8 elements");
+  if (int e = validate_kv(kv, D)) return e;
+  if (R == 0) return DGPT_OK;
+  const size_t need = dgpt_decode_attn_workspace_bytes(R, H, D, n_splits);
+  if (need > 0 && (workspace == nullptr || workspace_bytes < need)) {
+    set_error("decode_attn: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+    return DGPT_E_WORKSPACE;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const KvView view = make_view(kv);
+  float* ws = static_cast<float*>(workspace);
+#define DGPT_DEC(TT, DD)                                                                                         \
+  return decode_launch<TT, DD>(q, q_row_stride, view, len0, start1, len1, step_ptr, prefix_o, prefix_lse, gate, \
+                               gate_row_stride, y, y_row_stride, ws, n_splits, R, H, st)
+  if (dtype == DGPT_F32) {
+    switch (D) {
+      case 8: DGPT_DEC(float, 8);
+      case 16: DGPT_DEC(float, 16);
+      case 32: DGPT_DEC(float, 32);
+      case 64: DGPT_DEC(float, 64);
+      case 128: DGPT_DEC(float, 128);
+    }
+  } else if (dtype == DGPT_BF16) {
+    switch (D) {
+      case 8: DGPT_DEC(__nv_bfloat16, 8);
+      case 16: DGPT_DEC(__nv_bfloat16, 16);
+      case 32: DGPT_DEC(__nv_bfloat16, 32);
+      case 64: DGPT_DEC(__nv_bfloat16, 64);
+      case 128: DGPT_DEC(__nv_bfloat16, 128);
+      case 256: DGPT_DEC(__nv_bfloat16, 256);
+    }
+  }
+#undef DGPT_DEC
+  set_error("decode_attn: dtype %d with head_dim %d is not built", dtype, D);
+  return DGPT_E_UNSUPPORTED;
+}

@@ -1,0 +1,342 @@
+// Row-wise fused kernels: embedding gather + RMSNorm, Block-Attention-Residual
+// depth mix + RMSNorm, SwiGLU, logit soft-cap, and the host-side error plumbing.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace dgpt {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int launch_status(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return DGPT_E_CUDA;
+  }
+  return DGPT_OK;
+}
+
+// ---- embedding gather + RMSNorm ---------------------------------------------
+// One warp per token.  The row is read twice (second read hits L1/L2).
+template <typename T>
+__global__ void embed_rmsnorm_kernel(const int* __restrict__ ids, const T* __restrict__ emb,
+                                     T* __restrict__ out, long long n_tokens, int C, int V) {
+  const long long tok = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (tok >= n_tokens) return;
+  const int lane = threadIdx.x & 31;
+  int id = ids[tok];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  const T* row = emb + (long long)id * C;
+  float ss = 0.f;
+  for (int c = lane; c < C; c += 32) {
+    const float x = Io<T>::ld(row + c);
+    ss += x * x;
+  }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)C + kRmsEps);
+  T* o = out + tok * C;
+  for (int c = lane; c < C; c += 32) Io<T>::st(o + c, Io<T>::ld(row + c) * inv);
+}
+
+// ---- depth mix --------------------------------------------------------------
+constexpr int kMaxCands = 64;
+struct CandPtrs {
+  const void* p[kMaxCands];
+};
+
+// One warp per row, one pass over the candidates with an online softmax across
+// them: each candidate row is read exactly once and nothing is indexed
+// dynamically in registers.  Lane l owns elements l + 32*i  (i < EPL).
+template <typename T, int EPL>
+__global__ void depthmix_kernel(CandPtrs cands, int n_cands, const T* __restrict__ w,
+                                T* __restrict__ out_h, T* __restrict__ out_rn, long long rows, int C) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  float acc[EPL], wv[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    acc[i] = 0.f;
+    const int c = lane + 32 * i;
+    wv[i] = (n_cands > 1 && c < C) ? Io<T>::ld(w + c) : 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  for (int n = 0; n < n_cands; ++n) {
+    const T* src = static_cast<const T*>(cands.p[n]) + row * C;
+    float v[EPL];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int c = lane + 32 * i;
+      v[i] = c < C ? Io<T>::ld(src + c) : 0.f;
+      ss += v[i] * v[i];
+    }
+    if (n_cands == 1) {
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) acc[i] = v[i];
+      l = 1.f;
+      break;
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)C + kRmsEps);
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) dot += Io<T>::round(v[i] * inv) * wv[i];
+    dot = Io<T>::round(warp_sum(dot));
+    const float m_new = fmaxf(m, dot);
+    const float resc = __expf(m - m_new);
+    const float p = __expf(dot - m_new);
+    l = l * resc + p;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) acc[i] = acc[i] * resc + p * v[i];
+    m = m_new;
+  }
+  const float invl = 1.f / l;
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    acc[i] = Io<T>::round(acc[i] * invl);
+    ss += acc[i] * acc[i];
+  }
+  if (out_h) {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int c = lane + 32 * i;
+      if (c < C) Io<T>::st(out_h + row * C + c, acc[i]);
+    }
+  }
+  if (out_rn) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)C + kRmsEps);
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int c = lane + 32 * i;
+      if (c < C) Io<T>::st(out_rn + row * C + c, acc[i] * inv);
+    }
+  }
+}
+
+template <typename T>
+static int depthmix_launch(const CandPtrs& cp, int n, const void* w, void* out_h, void* out_rn,
+                           long long rows, int C, cudaStream_t st) {
+  const int warps = 4;
+  const unsigned grid = (unsigned)((rows + warps - 1) / warps);
+  const int epl = (C + 31) / 32;
+#define DGPT_MIX(E)                                                                        \
+  depthmix_kernel<T, E><<<grid, warps * 32, 0, st>>>(cp, n, static_cast<const T*>(w),      \
+                                                     static_cast<T*>(out_h), static_cast<T*>(out_rn), rows, C)
+  if (epl <= 2) DGPT_MIX(2);
+  else if (epl <= 4) DGPT_MIX(4);
+  else if (epl <= 8) DGPT_MIX(8);
+  else if (epl <= 16) DGPT_MIX(16);
+  else if (epl <= 24) DGPT_MIX(24);
+  else if (epl <= 32) DGPT_MIX(32);
+  else if (epl <= 64) DGPT_MIX(64);
+  else {
+    set_error("depthmix: n_embd %d > 2048 is not built", C);
+    return DGPT_E_UNSUPPORTED;
+  }
+#undef DGPT_MIX
+  return launch_status("depthmix");
+}
+
+// ---- SwiGLU -----------------------------------------------------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ in, T* __restrict__ out, long long n_pairs, float alpha,
+                              float limit) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pairs) return;
+  float g = Io<T>::ld(in + 2 * i), lin = Io<T>::ld(in + 2 * i + 1);
+  g = fminf(g, limit);
+  lin = fminf(fmaxf(lin, -limit), limit);
+  // the reference materialises alpha*g, sigmoid(.), g*sig and lin+1 in the storage type
+  const float sg = Io<T>::round(1.f / (1.f + __expf(-Io<T>::round(alpha * g))));
+  const float a = Io<T>::round(g * sg);
+  Io<T>::st(out + i, a * Io<T>::round(lin + 1.f));
+}
+
+template <>
+__global__ void swiglu_kernel<__nv_bfloat16>(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                             long long n_pairs, float alpha, float limit) {
+  // 4 pairs (16 bytes in, 8 bytes out) per thread
+  const long long i4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i4 >= n_pairs) return;
+  using B = Io<__nv_bfloat16>;
+  if (i4 + 4 <= n_pairs) {
+    float x[8];
+    ld16<__nv_bfloat16>(in + 2 * i4, x);
+    __nv_bfloat16 r[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float g = fminf(x[2 * k], limit);
+      const float lin = fminf(fmaxf(x[2 * k + 1], -limit), limit);
+      const float sg = B::round(1.f / (1.f + __expf(-B::round(alpha * g))));
+      r[k] = __float2bfloat16_rn(B::round(g * sg) * B::round(lin + 1.f));
+    }
+    *reinterpret_cast<uint2*>(out + i4) = *reinterpret_cast<uint2*>(r);
+  } else {
+    for (long long i = i4; i < n_pairs; ++i) {
+      const float g = fminf(B::ld(in + 2 * i), limit);
+      const float lin = fminf(fmaxf(B::ld(in + 2 * i + 1), -limit), limit);
+      const float sg = B::round(1.f / (1.f + __expf(-B::round(alpha * g))));
+      B::st(out + i, B::round(g * sg) * B::round(lin + 1.f));
+    }
+  }
+}
+
+// ---- soft cap ---------------------------------------------------------------
+template <typename T>
+__global__ void softcap_kernel(T* x, long long n, float cap) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) Io<T>::st(x + i, cap * Io<T>::round(tanhf(Io<T>::round(Io<T>::ld(x + i) / cap))));
+}
+
+__global__ void step_advance_kernel(int* step, int delta) { *step += delta; }
+
+// ---- y *= sigmoid(gate) -------------------------------------------------------
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* y, long long y_stride, const T* __restrict__ gate, long long g_stride,
+                                    long long rows, int n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * n) return;
+  const long long r = i / n;
+  const int c = (int)(i - r * n);
+  const float sg = Io<T>::round(1.f / (1.f + __expf(-Io<T>::ld(gate + r * g_stride + c))));
+  T* p = y + r * y_stride + c;
+  Io<T>::st(p, Io<T>::ld(p) * sg);
+}
+
+}  // namespace dgpt
+
+using namespace dgpt;
+
+extern "C" {
+
+int dgpt_last_error(char* buf, size_t n) {
+  const size_t len = strlen(g_err);
+  if (buf && n) {
+    strncpy(buf, g_err, n - 1);
+    buf[n - 1] = 0;
+  }
+  return (int)len;
+}
+
+int dgpt_version(void) { return 1; }
+
+int dgpt_embed_rmsnorm(const int32_t* ids, const void* emb, void* out, int64_t n_tokens, int32_t C, int32_t V,
+                       int32_t dtype, void* stream) {
+  DGPT_REQUIRE(ids && emb && out, "embed_rmsnorm: NULL pointer");
+  DGPT_REQUIRE(n_tokens >= 0 && C > 0 && V > 0, "embed_rmsnorm: bad sizes");
+  if (n_tokens == 0) return DGPT_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int warps = 4;
+  const unsigned grid = (unsigned)((n_tokens + warps - 1) / warps);
+  if (dtype == DGPT_F32)
+    embed_rmsnorm_kernel<float><<<grid, warps * 32, 0, st>>>(ids, static_cast<const float*>(emb),
+                                                            static_cast<float*>(out), n_tokens, C, V);
+  else if (dtype == DGPT_BF16)
+    embed_rmsnorm_kernel<__nv_bfloat16><<<grid, warps * 32, 0, st>>>(
+        ids, static_cast<const __nv_bfloat16*>(emb), static_cast<__nv_bfloat16*>(out), n_tokens, C, V);
+  else {
+    set_error("embed_rmsnorm: unknown dtype %d", dtype);
+    return DGPT_E_UNSUPPORTED;
+  }
+  return launch_status("embed_rmsnorm");
+}
+
+int dgpt_depthmix(const void* const* cands, int32_t n_cands, const void* w, void* out_h, void* out_rn,
+                  int64_t rows, int32_t C, int32_t dtype, void* stream) {
+  DGPT_REQUIRE(cands && n_cands >= 1 && n_cands <= kMaxCands, "depthmix: n_cands must be in [1, %d]", kMaxCands);
+  DGPT_REQUIRE(n_cands == 1 || w, "depthmix: pseudo-query w is NULL");
+  DGPT_REQUIRE(out_h || out_rn, "depthmix: no output requested");
+  DGPT_REQUIRE(rows >= 0 && C > 0, "depthmix: bad sizes");
+  if (rows == 0) return DGPT_OK;
+  CandPtrs cp;
+  for (int i = 0; i < n_cands; ++i) {
+    DGPT_REQUIRE(cands[i], "depthmix: candidate %d is NULL", i);
+    cp.p[i] = cands[i];
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == DGPT_F32) return depthmix_launch<float>(cp, n_cands, w, out_h, out_rn, rows, C, st);
+  if (dtype == DGPT_BF16) return depthmix_launch<__nv_bfloat16>(cp, n_cands, w, out_h, out_rn, rows, C, st);
+  set_error("depthmix: unknown dtype %d", dtype);
+  return DGPT_E_UNSUPPORTED;
+}
+
+int dgpt_swiglu(const void* in, void* out, int64_t rows, int32_t n_out, float alpha, float limit, int32_t dtype,
+                void* stream) {
+  DGPT_REQUIRE(in && out, "swiglu: NULL pointer");
+  DGPT_REQUIRE(rows >= 0 && n_out > 0, "swiglu: bad sizes");
+  const long long n = (long long)rows * n_out;
+  if (n == 0) return DGPT_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == DGPT_F32) {
+    swiglu_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(static_cast<const float*>(in),
+                                                                     static_cast<float*>(out), n, alpha, limit);
+  } else if (dtype == DGPT_BF16) {
+    DGPT_REQUIRE((reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 7) == 0,
+                 "swiglu: bf16 buffers must be 16-byte aligned");
+    const long long nt = (n + 3) / 4;
+    swiglu_kernel<__nv_bfloat16><<<(unsigned)((nt + 255) / 256), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), n, alpha, limit);
+  } else {
+    set_error("swiglu: unknown dtype %d", dtype);
+    return DGPT_E_UNSUPPORTED;
+  }
+  return launch_status("swiglu");
+}
+
+int dgpt_softcap(void* logits, int64_t n, float cap, int32_t dtype, void* stream) {
+  DGPT_REQUIRE(logits && n >= 0 && cap >= 0.f, "softcap: bad arguments");
+  if (n == 0 || cap == 0.f) return DGPT_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (dtype == DGPT_F32)
+    softcap_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(logits), n, cap);
+  else if (dtype == DGPT_BF16)
+    softcap_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(logits), n, cap);
+  else {
+    set_error("softcap: unknown dtype %d", dtype);
+    return DGPT_E_UNSUPPORTED;
+  }
+  return launch_status("softcap");
+}
+
+int dgpt_step_advance(int32_t* step_ptr, int32_t delta, void* stream) {
+  DGPT_REQUIRE(step_ptr, "step_advance: NULL pointer");
+  step_advance_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(step_ptr, delta);
+  return launch_status("step_advance");
+}
+
+}  // extern "C"
+
+extern "C" int dgpt_sigmoid_gate(void* y, int64_t y_row_stride, const void* gate, int64_t gate_row_stride,
+                                 int64_t rows, int32_t n_cols, int32_t dtype, void* stream) {
+  DGPT_REQUIRE(y && gate && rows >= 0 && n_cols > 0, "sigmoid_gate: bad arguments");
+  const long long n = (long long)rows * n_cols;
+  if (n == 0) return DGPT_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (dtype == DGPT_F32)
+    sigmoid_gate_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(y), y_row_stride,
+                                                     static_cast<const float*>(gate), gate_row_stride, rows, n_cols);
+  else if (dtype == DGPT_BF16)
+    sigmoid_gate_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(y), y_row_stride,
+                                                             static_cast<const __nv_bfloat16*>(gate), gate_row_stride,
+                                                             rows, n_cols);
+  else {
+    set_error("sigmoid_gate: unknown dtype %d", dtype);
+    return DGPT_E_UNSUPPORTED;
+  }
+  return launch_status("sigmoid_gate");
+}

@@ -1,0 +1,185 @@
+/*
+ * dgpt.h — C ABI of libdgpt_b200.so: the sm_100a kernels behind diff-gpt's
+ * attention forward and KV-cache Monte-Carlo decode.
+ *
+ * Conventions
+ *   - Every pointer marked "device" is a CUDA device pointer owned by the caller
+ *     (inputs, outputs and workspaces alike); the library never allocates, frees
+ *     or keeps them, except where an entry point says otherwise.
+ *   - `stream` is the caller's cudaStream_t passed as void*.  All entry points
+ *     enqueue work and return without synchronising; they may be captured into
+ *     a CUDA graph.
+ *   - Return value 0 = enqueued; negative = DGPT_E_* (nothing was enqueued).
+ *     `dgpt_last_error` gives the text of the last failure on the calling thread.
+ *   - `dtype` selects the storage type of activations, weights and KV pages:
+ *     DGPT_F32 or DGPT_BF16.  Accumulation is always fp32.
+ *   - The reference has no FFI layer of its own (it is pure PyTorch); each entry
+ *     point names the reference Python call sites whose arithmetic it replaces
+ *     (paths are relative to the reference project root).
+ */
+#ifndef DGPT_H_
+#define DGPT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { DGPT_F32 = 0, DGPT_BF16 = 1 };
+
+enum {
+  DGPT_OK = 0,
+  DGPT_E_ARG = -1,      /* bad argument (shape, alignment, null pointer)            */
+  DGPT_E_UNSUPPORTED = -2, /* combination of dtype / head_dim not built               */
+  DGPT_E_CUDA = -3,     /* a CUDA runtime call failed at launch                      */
+  DGPT_E_WORKSPACE = -4 /* caller's workspace is too small                           */
+};
+
+/* Where the K and V vectors of one layer live.
+ * Token `slot` of sequence `seq`, head `h`, lives in page
+ *     pg = page_table ? page_table[seq * max_pages + slot / page_tokens] : seq
+ * at element offset  pg * page_stride + h * head_stride + (slot % page_tokens) * head_dim
+ * from k_base (keys) or v_base (values).
+ * The dense reference cache (L,2,B,H,T,D) of src/diff_gpt/model/kv_cache.py:25 is the
+ * special case page_table = NULL, page_tokens = T, page_stride = H*T*D, head_stride = T*D.
+ */
+typedef struct dgpt_kv_layout {
+  void* k_base;              /* device */
+  void* v_base;              /* device */
+  int64_t page_stride;       /* elements */
+  int64_t head_stride;       /* elements */
+  const int32_t* page_table; /* device, [n_seq][max_pages], or NULL */
+  int32_t page_tokens;
+  int32_t max_pages;
+} dgpt_kv_layout;
+
+/* Text of the last error raised on this host thread; returns its length. */
+int dgpt_last_error(char* buf, size_t n);
+
+/* ABI version (bumped when a signature changes). */
+int dgpt_version(void);
+
+/* x = rms_norm(Emb[ids]).
+ * Replaces src/diff_gpt/model/gpt.py:154-155.
+ * ids: device int32 [n_tokens]; emb: device [V, C]; out: device [n_tokens, C]. */
+int dgpt_embed_rmsnorm(const int32_t* ids, const void* emb, void* out, int64_t n_tokens, int32_t C,
+                       int32_t V, int32_t dtype, void* stream);
+
+/* Block Attention Residual depth mix, fused with the RMSNorm that follows it.
+ *   a_n   = softmax_n( rms_norm(cand_n) . w )          n = 0..n_cands-1
+ *   h     = sum_n a_n cand_n                            (written to out_h if non-NULL)
+ *   out_rn= rms_norm(h)                                 (written if non-NULL)
+ * With n_cands == 1 the mix is the identity (the layer-0 short-circuit), so the call
+ * degenerates to a plain RMSNorm — also used for the final norm before the logits.
+ * Replaces src/diff_gpt/model/block.py:10-44 plus the rms_norm of block.py:97,104
+ * and gpt.py:180.
+ * cands: HOST array of n_cands device pointers, each [rows, C] contiguous
+ * (duplicates allowed — the reference commits the embedding twice); w: device [C]. */
+int dgpt_depthmix(const void* const* cands, int32_t n_cands, const void* w, void* out_h, void* out_rn,
+                  int64_t rows, int32_t C, int32_t dtype, void* stream);
+
+/* RoPE on q and k, RMSNorm over head_dim on both, then append k and v to the cache.
+ *   token (s, t), s < n_seq, t < T:   position = seq_pos0[s] + step + t   (RoPE row)
+ *                                     slot     = seq_slot0[s] + step + t  (cache slot)
+ *   with step = *step_ptr (0 when step_ptr is NULL).
+ * Rounding follows the reference: the rotated vector is rounded to `dtype`, then
+ * normalised in fp32 and rounded again.
+ * Replaces src/diff_gpt/model/rope.py:20-27, mha.py:44-48 and kv_cache.py:108-109.
+ * q,k,v: device, rows of H*D elements, token row n = s*T + t at n*in_row_stride;
+ * q_out: device [n_seq*T, H*D] with row stride q_out_row_stride;
+ * cs_table: device [table_len, D/2, 2] (cos, sin) in `dtype`;
+ * status: device int32, set to 1 if a position or slot is out of range (the write is skipped). */
+int dgpt_rope_qknorm_kvappend(const void* q, const void* k, const void* v, int64_t in_row_stride,
+                              void* q_out, int64_t q_out_row_stride, const void* cs_table,
+                              int32_t table_len, const dgpt_kv_layout* kv, const int32_t* seq_pos0,
+                              const int32_t* seq_slot0, const int32_t* step_ptr, int32_t n_seq,
+                              int32_t T, int32_t H, int32_t D, int32_t dtype, int32_t* status,
+                              void* stream);
+
+/* Prefill / chunk attention:  o[b,i,h,:] = softmax_j( q[b,i,h,:].k[b,j,h,:] / sqrt(D) ) v[b,j,h,:]
+ * over cache slots j < kv_len (and j <= q_offset + i when `causal`).  That single rule covers the
+ * three SDPA branches of src/diff_gpt/model/mha.py:61-81.  When `lse` is non-NULL the natural-log
+ * sum of exponentials of the scaled scores is written too ([B, Tq, H] fp32), so the result can be merged
+ * with attention over further keys (the shared-prefix phase of the Monte-Carlo decode);
+ * in that mode `o` may be requested in fp32 (o_f32 != 0) regardless of `dtype`.
+ * q: device, element (b,i,h,d) at b*q_batch_stride + i*q_row_stride + h*D + d;  o likewise.
+ * kv: sequence index = b;  kv_len: device int32 [B] or NULL (then kv_len_all is used).
+ * impl: 0 = choose (bf16 with D = 64 or 128 runs on the tcgen05 tensor cores, everything else takes
+ * the warp-level online-softmax kernel), 1 = warp-level kernel, 2 = tensor-core kernel or fail.
+ * status: device int32, set non-zero if a bounded wait inside the tensor-core kernel ran out. */
+int dgpt_fmha_prefill(const void* q, int64_t q_batch_stride, int64_t q_row_stride,
+                      const dgpt_kv_layout* kv, const int32_t* kv_len, int32_t kv_len_all, void* o,
+                      int64_t o_batch_stride, int64_t o_row_stride, int32_t o_f32, float* lse,
+                      int32_t B, int32_t H, int32_t Tq, int32_t D, int32_t q_offset, int32_t causal,
+                      int32_t dtype, int32_t impl, int32_t* status, void* stream);
+
+/* Bytes of workspace dgpt_decode_attn needs for R rows, H heads, head_dim D and n_splits. */
+size_t dgpt_decode_attn_workspace_bytes(int32_t R, int32_t H, int32_t D, int32_t n_splits);
+
+/* Decode attention for one new token per row (Tq = 1), split along the keys.
+ * Row r attends to cache slots  [0, len0[r])  and  [start1[r], start1[r] + len1[r] + step)  of
+ * sequence r  (step = *step_ptr or 0).  If prefix_o / prefix_lse are given, range 0 has already been
+ * reduced by dgpt_fmha_prefill (shared-prefix phase) and is skipped here; its partial result is merged.
+ * The merged output is multiplied by sigmoid(gate) when gate is non-NULL.
+ * Replaces src/diff_gpt/model/mha.py:65-68 and :83-84.
+ * q, gate, y: device [R, H*D] with their row strides; workspace: device, from the _bytes call
+ * (unused when n_splits == 1). */
+int dgpt_decode_attn(const void* q, int64_t q_row_stride, const dgpt_kv_layout* kv, const int32_t* len0,
+                     const int32_t* start1, const int32_t* len1, const int32_t* step_ptr,
+                     const float* prefix_o, const float* prefix_lse, const void* gate,
+                     int64_t gate_row_stride, void* y, int64_t y_row_stride, void* workspace,
+                     size_t workspace_bytes, int32_t n_splits, int32_t R, int32_t H, int32_t D,
+                     int32_t dtype, void* stream);
+
+/* out[r, j] = g*sigmoid(alpha*g)*(l+1) with g = min(in[r,2j], limit), l = clamp(in[r,2j+1], -limit, limit).
+ * Replaces src/diff_gpt/model/swi_glu.py:11-19.  in: [rows, 2*n_out]; out: [rows, n_out]. */
+int dgpt_swiglu(const void* in, void* out, int64_t rows, int32_t n_out, float alpha, float limit,
+                int32_t dtype, void* stream);
+
+/* In-place y[r, c] *= sigmoid(gate[r, c]) — the output gate after prefill attention (the decode kernel
+ * applies it in its epilogue).  Replaces src/diff_gpt/model/mha.py:84.  y, gate: device [rows, n_cols]. */
+int dgpt_sigmoid_gate(void* y, int64_t y_row_stride, const void* gate, int64_t gate_row_stride,
+                      int64_t rows, int32_t n_cols, int32_t dtype, void* stream);
+
+/* In-place logits = cap * tanh(logits / cap) (no-op when cap == 0).
+ * Replaces src/diff_gpt/model/gpt.py:182-186.  logits: device [n] */
+int dgpt_softcap(void* logits, int64_t n, float cap, int32_t dtype, void* stream);
+
+/* *step_ptr += delta, as a one-thread kernel on `stream`: the last node of a captured decode step,
+ * so that replaying the same launch sequence walks through the positions.  (The reference keeps the
+ * position on the host: src/diff_gpt/model/kv_cache.py:113-115.) */
+int dgpt_step_advance(int32_t* step_ptr, int32_t delta, void* stream);
+
+/* Soft-cap, top-p filter and temperature sampling of one token per row, with teacher forcing.
+ *   z        = cap * tanh(logits / cap)                  (cap == 0: z = logits)
+ *   nucleus  = tokens whose probability mass BEFORE them, in descending softmax(z) order, is < top_p
+ *              (top_p >= 1 disables the filter, top_p <= 0 keeps only the top token; ties broken by lower id first)
+ *   token    = argmax z over the nucleus                 if temperature == 0
+ *            = inverse-CDF draw from softmax(z / temperature) over the nucleus, using one
+ *              Philox4x32-10 uniform keyed by (seed, traj_id0 + row, step + step_base)
+ *   f = force_schedule[(row / force_group_rows) * force_group_stride + step]   (one schedule per group of rows;
+ *       stride 0 = one schedule for all);  if force_schedule && f >= 0: token = f, mask = 0, else mask = 1
+ * step = *step_ptr (0 when NULL).  traj_ids (device int64 [R]) overrides traj_id0 + row when non-NULL.
+ * Replaces src/diff_gpt/model/gpt.py:182-186 (cap), sampler/temperature.py:21-25,
+ * sampler/nucleus.py:29-40 and the sample-or-force logic of model/engine.py:106-146.
+ * logits: device [R, V] with row stride; out_tokens/out_masks: device int32 [R] (masks may be NULL);
+ * history_tokens / history_masks: device int32 [R, history_stride] or NULL — column `step` is written. */
+int dgpt_sample(const void* logits, int64_t logits_row_stride, int32_t R, int32_t V, float cap,
+                float temperature, float top_p, uint64_t seed, int64_t traj_id0, const int64_t* traj_ids,
+                int32_t step_base, const int32_t* step_ptr, const int32_t* force_schedule,
+                int32_t force_group_rows, int64_t force_group_stride, int32_t* out_tokens, int32_t* out_masks, int32_t* history_tokens,
+                int32_t* history_masks, int64_t history_stride, int32_t dtype, void* stream);
+
+/* filtered = logits where the token is in the top-p set (same rule as dgpt_sample, no soft-cap), -inf elsewhere.
+ * Lets a top-p filter sit in front of an arbitrary inner sampler.
+ * Replaces src/diff_gpt/sampler/nucleus.py:29-39.  logits, filtered: device [R, V] with row strides. */
+int dgpt_nucleus_filter(const void* logits, int64_t logits_row_stride, void* filtered,
+                        int64_t filtered_row_stride, int32_t R, int32_t V, float top_p, int32_t dtype,
+                        void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DGPT_H_ */

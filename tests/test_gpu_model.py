@@ -1,0 +1,318 @@
+"""Model- and engine-level parity on the GPU against reference-generated fixtures and the CPU oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_weights, load_golden
+from oracle import ref_decode, ref_math
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(meta, weights, dtype, **kw):
+    from diff_gpt_b200 import GPT
+
+    V, C, H, L, block = (int(x) for x in meta[:5])
+    m = GPT(vocab_size=V, n_embd=C, block_size=block, n_head=H, n_layer=L, **kw).eval()
+    sd = dict(weights)
+    sd["lm_head.weight"] = sd["token_embedding_table.weight"]
+    m.load_state_dict(sd)
+    return m.to(dtype).cuda()
+
+
+def _shape(meta, **kw):
+    V, C, H, L, block = (int(x) for x in meta[:5])
+    return ref_math.Shape(vocab_size=V, n_embd=C, n_head=H, n_layer=L, block_size=block, **kw)
+
+
+CASES = [
+    ("small_fp32", torch.float32, 1e-4),
+    ("small_bf16_d64", torch.bfloat16, 2e-2),
+    ("small_bf16_d32", torch.bfloat16, 2e-2),
+]
+
+
+@pytest.mark.parametrize("name,dtype,tol", CASES)
+def test_forward_full_serial_chunked_vs_reference(name, dtype, tol):
+    """Full causal forward, token-by-token decode through a KVCache and chunked prefill all
+    reproduce the reference's logits (cf. reference tests test_gpt.py:34-76, test_mha.py:80-158)."""
+    from diff_gpt_b200 import KVCache
+
+    g = load_golden(name)
+    m = _model(g["meta"], golden_weights(g, torch.float32), dtype)
+    idx = torch.from_numpy(g["idx"]).cuda()
+    B, T = idx.shape
+    H, L, D = m.n_head, m.n_layer, m.n_embd // m.n_head
+    scale = np.abs(g["logits_full"]).max()
+    full, loss = m(idx)
+    assert loss is None and full.shape == g["logits_full"].shape and full.dtype == dtype
+    assert np.abs(full.float().cpu().numpy() - g["logits_full"]).max() <= tol * scale
+    kv = KVCache(batch_size=B, num_heads=H, seq_len=T, head_dim=D, num_layers=L)
+    serial = torch.cat([m(idx[:, t : t + 1], kv_cache=kv)[0] for t in range(T)], dim=1)
+    assert kv.get_pos() == T
+    assert np.abs(serial.float().cpu().numpy() - g["logits_serial"]).max() <= tol * scale
+    cut = int(g["meta"][7])
+    kv2 = KVCache(batch_size=B, num_heads=H, seq_len=T, head_dim=D, num_layers=L)
+    a, _ = m(idx[:, :cut], kv_cache=kv2)
+    b, _ = m(idx[:, cut:], kv_cache=kv2)
+    chunked = torch.cat([a, b], dim=1).float().cpu().numpy()
+    assert np.abs(chunked - g["logits_chunked"]).max() <= tol * scale
+    # cache contents: K after RoPE + QK-norm, V raw, reference layout (L, 2, B, H, T, D)
+    assert kv2.kv_cache.shape == g["kv_cache"].shape
+    kscale = np.abs(g["kv_cache"]).max()
+    assert np.abs(kv2.kv_cache.float().cpu().numpy() - g["kv_cache"]).max() <= (1e-5 if dtype == torch.float32 else 2e-2) * kscale
+
+
+def test_state_dict_keys_and_tying():
+    from diff_gpt_b200 import GPT
+
+    g = load_golden("small_fp32")
+    m = GPT(vocab_size=64, n_embd=32, block_size=16, n_head=4, n_layer=3)
+    ref_keys = {k[2:] for k in g if k.startswith("w:")} | {"lm_head.weight"}
+    assert set(m.state_dict().keys()) == ref_keys
+    assert m.lm_head.weight is m.token_embedding_table.weight
+    assert m.freqs_cis.shape == (32, 4, 2)
+    with pytest.raises(AssertionError):
+        GPT(vocab_size=100)  # not a multiple of pad_vocab_size_to
+
+
+def test_softcap_bounds_and_disable():
+    g = load_golden("small_fp32")
+    w = golden_weights(g, torch.float32)
+    idx = torch.from_numpy(g["idx"]).cuda()
+    m = _model(g["meta"], w, torch.float32, logit_softcap=2.0)
+    assert m(idx)[0].abs().max().item() <= 2.0
+    raw = _model(g["meta"], w, torch.float32, logit_softcap=0.0)(idx)[0]
+    want = ref_math.forward(_shape(g["meta"], logit_softcap=0.0), w, idx.cpu())
+    assert (raw.cpu() - want).abs().max().item() <= 1e-4 * want.abs().max().item()
+
+
+def test_layers_per_block_two_matches_oracle_generalisation():
+    """Commit every second layer: compare with a direct restatement of block.py:74-107."""
+    g = load_golden("small_fp32")
+    w = golden_weights(g, torch.float32)
+    shape = _shape(g["meta"])
+    idx = torch.from_numpy(g["idx"])
+    m = _model(g["meta"], w, torch.float32, attn_res_layers_per_block=2)
+    got = m(idx.cuda())[0].cpu()
+    # restatement with a commit schedule
+    table = ref_math.rope_table(shape.head_dim, 2 * shape.block_size)
+    cs = table[: idx.shape[1]]
+    x = ref_math.rms_norm(w["token_embedding_table.weight"][idx])
+    blocks, partial = [x], x
+    for i in range(shape.n_layer):
+        pre = f"blocks.{i}."
+        h = x if (len(blocks) == 1 and partial is x) else ref_math.depth_mix(blocks + [partial], w[pre + "attn_res_proj.weight"])
+        if (i + 1) % 2 == 0:
+            blocks, partial = blocks + [partial], None
+        a = ref_math.attention_layer(shape, w, i, ref_math.rms_norm(h), cs, None)
+        partial = a if partial is None else partial + a
+        h2 = ref_math.depth_mix(blocks + [partial], w[pre + "mlp_res_proj.weight"])
+        partial = partial + ref_math.feed_forward(shape, w, i, ref_math.rms_norm(h2))
+    want = 15 * torch.tanh(ref_math.rms_norm(partial) @ w["token_embedding_table.weight"].T / 15)
+    assert (got - want).abs().max().item() <= 1e-4 * want.abs().max().item()
+
+
+def test_config1_teacher_forced_logits_and_argmax_stream():
+    """BASELINE config 1: drive the engine with the reference's own argmax stream as a force
+    schedule and compare every step's logits; then free-run argmax and compare the streams."""
+    from diff_gpt_b200 import Engine, TemperatureSampler
+    from diff_gpt_b200.model.engine import DecodeRun
+
+    g = load_golden("cfg1_fp32")
+    m = _model(g["meta"], golden_weights(g, torch.float32), torch.float32)
+    prompt = g["prompt"].tolist()
+    stream = g["argmax_stream"].tolist()
+    ref_logits = g["step_logits"]
+    G = len(stream)
+    run = DecodeRun(m, [prompt], 4, G, TemperatureSampler(0.0), 42, [stream], use_graph=False)
+    run.start()
+    got = [15 * torch.tanh(run.logits0[0].float() / 15).cpu().numpy()]
+    for _ in range(G - 1):
+        run.advance(1)
+        lg = run.plan.logits[0].float()
+        got.append((15 * torch.tanh(lg / 15)).cpu().numpy())
+    got = np.stack(got)
+    assert np.abs(got - ref_logits).max() <= 1e-4 * np.abs(ref_logits).max()
+    assert run.history.cpu()[:, :G].tolist() == [stream] * 4
+    # free-running argmax: identical stream (the fixture's top-2 gaps are far above 1e-4 relative)
+    top2 = np.sort(ref_logits, axis=-1)[:, -2:]
+    assert (top2[:, 1] - top2[:, 0]).min() > 1e-4 * np.abs(ref_logits).max()
+    res, masks = Engine(m).generate_batch(prompt, num_samples=3, max_tokens=G, sampler=TemperatureSampler(0.0))
+    assert all(r[: len(prompt)] == prompt and r[len(prompt) :] == stream for r in res)
+    assert all(mk == [0] * len(prompt) + [1] * G for mk in masks)
+
+
+def test_engine_force_schedule_fixture():
+    from diff_gpt_b200 import Engine, TemperatureSampler
+
+    g = load_golden("engine_force")
+    m = _model(g["meta"], golden_weights(g, torch.float32), torch.float32)
+    sched = [None if s < 0 else int(s) for s in g["sched"]]
+    res, masks = Engine(m).generate_batch(
+        g["prompt"].tolist(), num_samples=3, max_tokens=10, sampler=TemperatureSampler(0.0), force_schedule=sched
+    )
+    assert np.array_equal(np.asarray(res), g["results"])
+    assert np.array_equal(np.asarray(masks), g["masks"])
+
+
+def test_engine_streaming_equals_batch_and_graph_equals_eager():
+    from diff_gpt_b200 import Engine, NucleusSampler, TemperatureSampler
+
+    g = load_golden("small_bf16_d64")
+    m = _model(g["meta"], golden_weights(g, torch.float32), torch.bfloat16)
+    prompt = g["idx"][0].tolist()
+    s = NucleusSampler(0.9, TemperatureSampler(1.0))
+    eng = Engine(m)
+    res, _ = eng.generate_batch(prompt, num_samples=40, max_tokens=19, sampler=s, seed=7)
+    cols = list(eng.generate(prompt, num_samples=40, max_tokens=19, sampler=s, seed=7))
+    assert len(cols) == 19
+    streamed = np.asarray([c[0] for c in cols]).T
+    assert np.array_equal(streamed, np.asarray(res)[:, len(prompt) :])
+    t_graph, _ = eng.generate_many([prompt], 40, 19, s, seed=7, use_graph=True)
+    t_eager, _ = eng.generate_many([prompt], 40, 19, s, seed=7, use_graph=False)
+    assert torch.equal(t_graph, t_eager)
+    assert torch.equal(t_graph[0].cpu(), torch.tensor(res)[:, len(prompt) :].int())
+    other, _ = eng.generate_many([prompt], 40, 19, s, seed=8)
+    assert not torch.equal(other, t_graph)
+    assert len({tuple(r) for r in t_graph[0].cpu().tolist()}) > 1
+
+
+def test_engine_validation_and_ceiling():
+    from diff_gpt_b200 import Engine, TemperatureSampler
+
+    g = load_golden("small_fp32")
+    m = _model(g["meta"], golden_weights(g, torch.float32), torch.float32)  # block_size 16 -> ceiling 32
+    eng = Engine(m)
+    with pytest.raises(AssertionError, match="non-empty"):
+        eng.generate_batch([], num_samples=1, max_tokens=2)
+    with pytest.raises(AssertionError, match="list of ints"):
+        eng.generate_batch([1.5, 2], num_samples=1, max_tokens=2)
+    with pytest.raises(AssertionError, match="force_schedule must cover"):
+        eng.generate_batch([1, 2, 3], num_samples=1, max_tokens=5, force_schedule=[None, 1])
+    res, _ = eng.generate_batch(list(range(30)), num_samples=2, max_tokens=10, sampler=TemperatureSampler(0.0))
+    assert all(len(r) == 32 for r in res)  # clamped to 2 * block_size
+    res, _ = eng.generate_batch(list(range(32)), num_samples=2, max_tokens=10)
+    assert all(len(r) == 32 for r in res)  # nothing to generate
+
+
+def test_prefill_once_equals_independent_runs_and_shared_prefix_phase():
+    """N trajectories from one prefill equal N single runs under argmax (reference test_engine.py:301-347);
+    with >= 16 trajectories the shared-prefix phase is active and must give the same tokens."""
+    from diff_gpt_b200 import Engine, TemperatureSampler
+
+    g = load_golden("small_bf16_d32")
+    w = golden_weights(g, torch.float32)
+    m = _model(g["meta"], w, torch.float32)
+    prompt = g["idx"][1].tolist()
+    eng = Engine(m)
+    one, _ = eng.generate_batch(prompt, num_samples=1, max_tokens=12, sampler=TemperatureSampler(0.0))
+    many, _ = eng.generate_batch(prompt, num_samples=20, max_tokens=12, sampler=TemperatureSampler(0.0))
+    assert all(r == one[0] for r in many)
+    shape = _shape(g["meta"])
+    ref, _, _ = ref_decode.mc_decode(shape, w, prompt, 1, 12, temperature=0.0)
+    assert one[0][len(prompt) :] == ref[0].tolist()
+
+
+def test_multi_series_batch_equals_single_series_runs():
+    from diff_gpt_b200 import Engine, NucleusSampler, TemperatureSampler
+
+    g = load_golden("small_bf16_d32")
+    m = _model(g["meta"], golden_weights(g, torch.float32), torch.float32)
+    prompts = [g["idx"][0].tolist(), g["idx"][1].tolist()[:7], g["idx"][2].tolist()]
+    s = NucleusSampler(0.8, TemperatureSampler(1.3))
+    eng = Engine(m)
+    toks, masks = eng.generate_many(prompts, 18, 9, s, seed=3)
+    assert toks.shape == (3, 18, 9) and bool((masks == 1).all())
+    for i, p in enumerate(prompts):
+        solo, _ = eng.generate_many([p], 18, 9, s, seed=3, series_offset=i)
+        assert torch.equal(solo[0], toks[i]), i
+    # a shard of the trajectories reproduces its slice of the full run
+    part, _ = eng.generate_many(prompts, 6, 9, s, seed=3, traj_offset=12)
+    assert torch.equal(part, toks[:, 12:18])
+    # per-series force schedules
+    sch = [[None, 5, None] + [None] * 6, [7, None, None] + [None] * 6, [None] * 9]
+    ft, fm = eng.generate_many(prompts, 18, 9, s, seed=3, force_schedules=sch)
+    assert bool((ft[0, :, 1] == 5).all()) and bool((ft[1, :, 0] == 7).all())
+    assert fm[0, 0].tolist() == [1, 0, 1, 1, 1, 1, 1, 1, 1] and fm[2, 0].tolist() == [1] * 9
+
+
+def test_python_callable_sampler_sees_device_logits():
+    from diff_gpt_b200 import Engine
+
+    g = load_golden("small_fp32")
+    w = golden_weights(g, torch.float32)
+    m = _model(g["meta"], w, torch.float32)
+    seen = []
+
+    def pick(logits, rng=None):
+        assert logits.is_cuda and logits.shape == (3, 64)
+        seen.append(logits.float().cpu())
+        return torch.argmax(logits, dim=-1, keepdim=True)
+
+    prompt = [3, 1, 4, 1, 5]
+    res, masks = Engine(m).generate_batch(prompt, num_samples=3, max_tokens=6, sampler=pick)
+    ref, _, ref_logits = ref_decode.mc_decode(_shape(g["meta"]), w, prompt, 3, 6, temperature=0.0, keep_logits=True)
+    assert torch.tensor(res)[:, 5:].tolist() == ref.tolist()
+    got = torch.stack(seen)
+    assert (got - ref_logits).abs().max().item() <= 1e-4 * ref_logits.abs().max().item()
+
+
+def test_samplers_standalone_contract():
+    """Shape (B,1) int64, seeded determinism, T=0 == argmax, p -> 0 == argmax, p = 1 == inner sampler
+    (reference tests/diff_gpt/sampler/*.py)."""
+    from diff_gpt_b200 import NucleusSampler, TemperatureSampler
+
+    logits = torch.randn(4, 50, generator=torch.Generator().manual_seed(0)).cuda()
+    for s in (TemperatureSampler(1.0), NucleusSampler(0.9, TemperatureSampler(1.5))):
+        out = s(logits)
+        assert out.shape == (4, 1) and out.dtype == torch.int64
+        a = s(logits, rng=torch.Generator(device="cuda").manual_seed(42))
+        b = s(logits, rng=torch.Generator(device="cuda").manual_seed(42))
+        assert torch.equal(a, b)
+        many = [s(logits, rng=torch.Generator().manual_seed(k)) for k in range(12)]
+        assert any(not torch.equal(many[0], x) for x in many[1:])
+    am = torch.argmax(logits, -1, keepdim=True)
+    assert torch.equal(TemperatureSampler(0.0)(logits), am)
+    assert torch.equal(NucleusSampler(1e-9, TemperatureSampler(1.0))(logits), am)
+    assert torch.equal(NucleusSampler(0.5, TemperatureSampler(0.0))(logits), am)
+    r1 = NucleusSampler(1.0, TemperatureSampler(1.0))(logits, rng=torch.Generator().manual_seed(5))
+    r2 = TemperatureSampler(1.0)(logits, rng=torch.Generator().manual_seed(5))
+    assert torch.equal(r1, r2)
+    # a foreign inner sampler receives -inf outside the nucleus
+    probs = torch.tensor([[0.6, 0.25, 0.1, 0.05]]).log().cuda()
+
+    class Inner:
+        def __call__(self, lg, rng=None):
+            self.lg = lg
+            return torch.argmax(lg, -1, keepdim=True)
+
+    inner = Inner()
+    NucleusSampler(0.9, inner)(probs)
+    assert torch.isfinite(inner.lg).cpu().tolist() == [[True, True, True, False]]
+
+
+def test_kv_cache_reference_surface():
+    """Lazy allocation, growth in multiples of 1024, pos on the last layer only, batch broadcast, reset
+    (reference tests/diff_gpt/model/test_kv_cache.py)."""
+    from diff_gpt_b200 import KVCache
+
+    c = KVCache(batch_size=2, num_heads=2, seq_len=4, head_dim=8, num_layers=2)
+    assert c.kv_cache.numel() == 0 and c.get_pos() == 0
+    k = torch.randn(2, 2, 3, 8, device="cuda")
+    kk, vv = c.insert_kv(0, k, k * 2)
+    assert c.get_pos() == 0 and kk.shape == (2, 2, 3, 8)
+    c.insert_kv(1, k, k)
+    assert c.get_pos() == 3
+    c.insert_kv(0, k, k)  # 6 > 4: grow to (6 + 1024) rounded up to 1024 = 2048
+    assert c.kv_cache.shape[4] == 2048 and c.kv_shape[4] == 2048
+    assert torch.equal(c.kv_cache[0, 0, :, :, :3], k) and torch.equal(c.kv_cache[0, 1, :, :, :3], k * 2)
+    one = KVCache(batch_size=1, num_heads=2, seq_len=3, head_dim=8, num_layers=2)
+    one.insert_kv(0, k[:1], k[:1])
+    one.insert_kv(1, k[:1], k[:1])
+    wide = KVCache(batch_size=5, num_heads=2, seq_len=9, head_dim=8, num_layers=2)
+    wide.prefill(one)
+    assert wide.get_pos() == 3 and torch.equal(wide.kv_cache[1, 0, 4, :, :3], k[0])
+    wide.reset()
+    assert wide.get_pos() == 0
