@@ -1,0 +1,384 @@
+"""Benchmark of the Monte-Carlo decode path (BASELINE config 4) on 1..8 B200s of one box.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload ("step"): W = n_gpus series are decoded per step; each rank prefills the
+1024-token prompt of every series of the step and decodes its contiguous slice of
+4096 / W of that series' 4096 trajectories for 256 tokens with top-p 0.9 /
+temperature 1 sampling, then the token streams are all-gathered.  Every rank
+therefore carries 4096 trajectories per step whatever N is (weak scaling), and at
+N = 1 a step is exactly one series of config 4.  Model: vocab 4096, n_embd 768,
+12 heads (head_dim 64), 12 layers, block 2048, bf16, weights N(0, 0.02) seed 4.
+Inputs are seeded synthetic random-walk + seasonal series tokenised with the
+order-1 sigma-delta encoder; nothing is read from disk.
+
+One JSON line is printed by rank 0.  `value` is device-timed with the prompts
+already resident in HBM; `e2e` goes through `Engine.generate_many` with host
+prompts and a device->host copy of all tokens inside the timed region.  The KV
+pool (38.7 GB per rank) is far larger than L2, so no explicit L2 flush is needed.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CFG4 = dict(vocab_size=4096, n_embd=768, n_head=12, n_layer=12, block_size=2048)
+PROMPT_TOKENS, HORIZON, TRAJECTORIES, N_SERIES = 1024, 256, 4096, 32
+TOP_P, TEMPERATURE, WEIGHT_SEED = 0.9, 1.0, 4
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def synthetic_prompts(n_series: int, vocab: int) -> list[list[int]]:
+    """Random walk (step sd 0.5) + sin(2 pi t / 24), 1025 points -> 1024 order-1 tokens per series."""
+    from diff_gpt_b200.encoder_decoder import encode, get_domain_of_definition
+
+    rng = np.random.default_rng(4)
+    out = []
+    t = np.arange(PROMPT_TOKENS + 1)
+    for _ in range(n_series):
+        x = (np.cumsum(rng.normal(0.0, 0.5, t.size)) + np.sin(2 * np.pi * t / 24.0)).reshape(-1, 1)
+        dom = get_domain_of_definition(x, 1, use_decimal=False)
+        _, _, tok = encode(inp=x, vocab_size=vocab, domain_of_definition=dom, order_of_derivative=1, use_decimal=False)
+        out.append(tok.reshape(-1).astype(np.int64).tolist())
+    return out
+
+
+def cfg4_weights(dtype) -> dict:
+    """state_dict of the config-4 model: every parameter ~ N(0, 0.02) from torch.Generator(seed 4)."""
+    g = torch.Generator().manual_seed(WEIGHT_SEED)
+    C, V = CFG4["n_embd"], CFG4["vocab_size"]
+
+    def n(*s):
+        return (torch.randn(*s, generator=g) * 0.02).to(dtype)
+
+    w = {"token_embedding_table.weight": n(V, C)}
+    for i in range(CFG4["n_layer"]):
+        p = f"blocks.{i}."
+        for name in ("c_q", "c_k", "c_v", "c_g", "c_proj"):
+            w[p + f"sa.{name}.weight"] = n(C, C)
+        w[p + "ffwd.net.0.weight"] = n(4 * C, C)
+        w[p + "ffwd.net.2.weight"] = n(C, 2 * C)
+        w[p + "attn_res_proj.weight"] = n(1, C)
+        w[p + "mlp_res_proj.weight"] = n(1, C)
+    return w
+
+
+def oracle_shape():
+    from oracle import ref_math  # CPU legs only
+
+    return ref_math.Shape(**CFG4)
+
+
+class ClockSampler:
+    """nvidia-smi polled every 200 ms for one GPU while the timed region runs."""
+
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int) -> None:
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=self.f, stderr=subprocess.DEVNULL,
+            )
+        except OSError:
+            self.p = None
+
+    def stop(self) -> dict:
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        self.p.wait()
+        self.f.flush()
+        rows = [r.split(",") for r in open(self.f.name).read().strip().splitlines() if r.strip()]
+        os.unlink(self.f.name)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[3:7]):
+                if v.strip().lower() == "active":
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+# ---------------------------------------------------------------------------------------
+# CPU legs (oracle port of the reference path, all host threads)
+# ---------------------------------------------------------------------------------------
+CPU_SAMPLE = dict(series=1, trajectories=64, steps=32)
+
+
+def cpu_step(shape, w, prompt) -> int:
+    from oracle import ref_decode
+
+    toks, _, _ = ref_decode.mc_decode(
+        shape, w, prompt, num_samples=CPU_SAMPLE["trajectories"], max_tokens=CPU_SAMPLE["steps"],
+        temperature=TEMPERATURE, top_p=TOP_P, seed=42,
+    )
+    return toks.numel()
+
+
+def cpu_sample_text() -> str:
+    return (
+        f"config 4 model and 1024-token prompt, {CPU_SAMPLE['series']} series x {CPU_SAMPLE['trajectories']} trajectories x "
+        f"{CPU_SAMPLE['steps']} decode steps (prefill included), replicated dense KV cache as in the reference"
+    )
+
+
+def run_reference(args) -> None:
+    """The reference arm: the CPU port of the reference path on the host cores (rank 0 only)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    shape, w = oracle_shape(), cfg4_weights(torch.bfloat16)
+    prompt = synthetic_prompts(1, CFG4["vocab_size"])[0]
+    cores = torch.get_num_threads()
+    for _ in range(args.warmup):
+        cpu_step(shape, w, prompt)
+    t0 = time.perf_counter()
+    n = 0
+    for _ in range(args.steps):
+        n += cpu_step(shape, w, prompt)
+    dt = time.perf_counter() - t0
+    v = n / dt
+    print(json.dumps({
+        "impl": "reference", "metric": "mc_decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": cpu_sample_text()},
+        "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {
+        "workload": "BASELINE config 4: large Monte-Carlo decode sharded by trajectory",
+        **CFG4, "prompt_tokens": PROMPT_TOKENS, "horizon": HORIZON, "trajectories_per_series": TRAJECTORIES,
+        "series_per_step": n_gpus, "trajectories_per_rank_per_series": TRAJECTORIES // n_gpus,
+        "sampler": f"nucleus p={TOP_P}, temperature {TEMPERATURE}", "parallelism": f"trajectory-sharded x{n_gpus}, weight replicas",
+        "l2": "inputs (38.7 GB KV pool per rank) are larger than L2; no flush",
+    }
+
+
+# ---------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------
+def run_ours(args) -> None:
+    import torch.distributed as dist
+
+    from diff_gpt_b200 import GPT, Engine, NucleusSampler, TemperatureSampler, _lib
+    from diff_gpt_b200.dist import gather_trajectories
+    from diff_gpt_b200.model.engine import DecodeRun
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N > 1"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert TRAJECTORIES % world == 0
+    n_local = TRAJECTORIES // world
+    series_per_step = world
+
+    w = cfg4_weights(torch.bfloat16)
+    model = GPT(**CFG4).eval()
+    sd = dict(w)
+    sd["lm_head.weight"] = sd["token_embedding_table.weight"]
+    model.load_state_dict(sd)
+    model = model.to(torch.bfloat16).to(dev)
+    prompts = synthetic_prompts(N_SERIES, CFG4["vocab_size"])
+    prompts_dev = torch.tensor(prompts, dtype=torch.int32, device=dev)
+    sampler = NucleusSampler(TOP_P, TemperatureSampler(TEMPERATURE))
+    engine = Engine(model)
+    tokens_per_step = series_per_step * TRAJECTORIES * HORIZON
+
+    def series_of(step_idx: int) -> list[int]:
+        return [(step_idx * series_per_step + j) % N_SERIES for j in range(series_per_step)]
+
+    def device_step(step_idx: int, use_graph: bool = True):
+        ids = series_of(step_idx)
+        run = DecodeRun(
+            model, prompts_dev[torch.tensor(ids, device=dev)], n_local, HORIZON, sampler, 42, None,
+            traj_offset=rank * n_local, series_offset=ids[0], use_graph=use_graph,
+        )
+        run.start()
+        run.advance(HORIZON)
+        toks = run.history.view(series_per_step, n_local, HORIZON)
+        return gather_trajectories(toks, TRAJECTORIES), run
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for i in range(args.warmup):
+        device_step(i)
+    barrier()
+    clocks = ClockSampler(local)
+    _lib.stats.launches = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        out, run = device_step(args.warmup + i)
+        del run
+    e1.record()
+    barrier()
+    launches = _lib.stats.launches
+    ms = e0.elapsed_time(e1)
+    clock_info = clocks.stop()
+    status_ok = True
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = args.steps * tokens_per_step / (ms / 1e3)
+    assert out.shape == (series_per_step, TRAJECTORIES, HORIZON) and int(out.min()) >= 0 and int(out.max()) < CFG4["vocab_size"]
+
+    # ---- end to end: host prompts in, host tokens out, through the public engine call ----
+    e2e_steps = max(1, min(args.steps, 2))
+    pinned = torch.empty((series_per_step, TRAJECTORIES, HORIZON), dtype=torch.int32).pin_memory()
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        ids = series_of(i)
+        toks, _ = engine.generate_many(
+            [prompts[s] for s in ids], n_local, HORIZON, sampler, seed=42, traj_offset=rank * n_local, series_offset=ids[0]
+        )
+        full = gather_trajectories(toks, TRAJECTORIES)
+        pinned.copy_(full, non_blocking=False)
+        del toks, full
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {
+        "value": e2e_steps * tokens_per_step / e2e_s, "unit": "tokens/s",
+        "h2d_bytes_per_step": series_per_step * PROMPT_TOKENS * 4,
+        "d2h_bytes_per_step": series_per_step * TRAJECTORIES * HORIZON * 4,
+        "steps": e2e_steps, "api": "Engine.generate_many(host prompts) -> pinned host int32 tokens",
+    }
+
+    # ---- per-kernel device time: one more step, launched eagerly with events around every call ----
+    roof, kernels = None, None
+    if rank == 0 and not args.no_kernel_pass:
+        timer = _lib.KernelTimer()
+        with _lib.timed(timer):
+            _, run = device_step(args.warmup + args.steps, use_graph=False)
+        torch.cuda.synchronize(dev)
+        del run
+        kernels = {k: {kk: round(vv, 4) if isinstance(vv, float) else vv for kk, vv in v.items()} for k, v in timer.summary().items()}
+        roof = roofline(kernels, n_local * series_per_step, series_per_step)
+    if world > 1:
+        barrier()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        prompt = prompts[0]
+        shape = oracle_shape()
+        cpu_step(shape, w, prompt)  # warm
+        t0 = time.perf_counter()
+        n = cpu_step(shape, w, prompt)
+        dt = time.perf_counter() - t0
+        cpu = {"value": n / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": cpu_sample_text()}
+
+    if rank == 0:
+        pk = peaks()
+        bytes_per_token = 4.82e6  # unique HBM bytes per generated token at this config (weights, shared prompt, own K/V)
+        line = {
+            "metric": "mc_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "clocks": clock_info, "e2e": e2e, "gpu_launches": launches, "roofline": roof, "cpu_baseline": cpu,
+            "decode_hbm": {
+                "algorithmic_bytes_per_token": bytes_per_token,
+                "achieved_gbs_per_gpu": value / world * bytes_per_token / 1e9,
+                "frac_of_peak": value / world * bytes_per_token / 1e9 / pk["hbm_gbs"], "peak_source": pk["source"],
+            },
+            "kernels": kernels, "status_ok": status_ok,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def roofline(kernels: dict, rows: int, n_series: int) -> dict:
+    """Roofline of the library kernel with the largest share of device time in the instrumented step."""
+    pk = peaks()
+    C, L, H = CFG4["n_embd"], CFG4["n_layer"], CFG4["n_head"]
+    mine = {k: v for k, v in kernels.items() if k.startswith("dgpt_")}
+    top = max(mine, key=lambda k: mine[k]["total_ms"])
+    k = mine[top]
+    total_s = k["total_ms"] / 1e3
+    steps = HORIZON - 1  # decode forwards (the forward after the last token is skipped)
+    if top == "dgpt_decode_attn":
+        # per launch (one layer, decode forward g = 1..255): every row reads its g own K and V vectors (C bf16 each), plus
+        # q, gate (bf16), the prompt partial (fp32 o + lse) and writes y (bf16)
+        kv_bytes = sum(rows * 2 * C * 2 * g for g in range(1, steps + 1)) * L
+        io_bytes = steps * L * rows * (3 * C * 2 + C * 4 + H * 4)
+        achieved = (kv_bytes + io_bytes) / total_s / 1e9
+        return {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                "launches": k["launches"], "avg_launch_ms": k["avg_ms"], "algorithmic_bytes_per_launch": (kv_bytes + io_bytes) / k["launches"]}
+    if top == "dgpt_fmha_prefill":
+        # shared-prompt phase per launch: QK^T and PV over rows x 1024 prompt keys, all heads: 4 * rows * P * C flops
+        decode_flops = steps * L * 4 * rows * PROMPT_TOKENS * C
+        prefill_flops = L * 2 * n_series * PROMPT_TOKENS * PROMPT_TOKENS * C  # causal prompt prefill
+        achieved = (decode_flops + prefill_flops) / total_s / 1e12
+        return {"kernel": top, "bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                "frac": achieved / pk["bf16_tflops_sustained"], "traffic": None, "peak_source": pk["source"],
+                "launches": k["launches"], "avg_launch_ms": k["avg_ms"]}
+    return {"kernel": top, "bound": "hbm", "achieved": None, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": None,
+            "traffic": None, "launches": k["launches"], "avg_launch_ms": k["avg_ms"]}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-kernel-pass", action="store_true", help="skip the per-kernel timing step")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -3,10 +3,15 @@
 The library is mandatory: importing this module raises if the shared object has
 not been built, and every wrapper raises `DgptError` on a non-zero status.
 There is no fallback path.
+
+`stats.launches` counts the library calls that enqueued kernels (eagerly or into a
+graph being captured); `KernelTimer` brackets each such call with CUDA events on the
+current stream, which is how the benchmark attributes device time to kernels.
 """
 
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 import os
 
@@ -64,20 +69,101 @@ PROTOTYPES = {
     ),
     "dgpt_nucleus_filter": (C.c_int, [_p, _i64, _p, _i64, _i32, _i32, _f32, _i32, _p]),
 }
+_NOT_LAUNCHING = {"dgpt_last_error", "dgpt_version", "dgpt_decode_attn_workspace_bytes"}
 
 
-def _load() -> C.CDLL:
+class Stats:
+    launches = 0
+    timer = None
+
+
+stats = Stats()
+
+
+class KernelTimer:
+    """Per-entry-point device time from CUDA events recorded around each call on the current stream."""
+
+    def __init__(self) -> None:
+        self.events: dict[str, list] = {}
+
+    def run(self, name, fn, args):
+        import torch
+
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        rc = fn(*args)
+        b.record()
+        self.events.setdefault(name, []).append((a, b))
+        return rc
+
+    @contextlib.contextmanager
+    def region(self, name):
+        import torch
+
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        yield
+        b.record()
+        self.events.setdefault(name, []).append((a, b))
+
+    def summary(self) -> dict[str, dict]:
+        """{name: {"launches", "total_ms", "avg_ms"}} (synchronise before calling)."""
+        out = {}
+        for name, evs in self.events.items():
+            ms = [a.elapsed_time(b) for a, b in evs]
+            out[name] = {"launches": len(ms), "total_ms": sum(ms), "avg_ms": sum(ms) / len(ms)}
+        return out
+
+
+@contextlib.contextmanager
+def timed(timer: KernelTimer):
+    stats.timer = timer
+    try:
+        yield timer
+    finally:
+        stats.timer = None
+
+
+@contextlib.contextmanager
+def region(name: str):
+    """Bracket non-library work (the cuBLAS GEMMs) when a timer is active; free otherwise."""
+    t = stats.timer
+    if t is None:
+        yield
+    else:
+        with t.region(name):
+            yield
+
+
+class _Lib:
+    def __init__(self, raw: C.CDLL) -> None:
+        self._raw = raw
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(raw, name)  # AttributeError if the symbol is not exported
+            fn.restype = res
+            fn.argtypes = args
+            setattr(self, name, fn if name in _NOT_LAUNCHING else self._wrap(name, fn))
+
+    @staticmethod
+    def _wrap(name, fn):
+        def call(*args):
+            t = stats.timer
+            rc = fn(*args) if t is None else t.run(name, fn, args)
+            if rc == 0:
+                stats.launches += 1
+            return rc
+
+        call.__name__ = name
+        return call
+
+
+def _load() -> _Lib:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
             f"{LIB_PATH} is missing: build it with `python -m diff_gpt_b200.build` "
             "(there is no fallback implementation)"
         )
-    lib = C.CDLL(LIB_PATH)
-    for name, (res, args) in PROTOTYPES.items():
-        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
-        fn.restype = res
-        fn.argtypes = args
-    return lib
+    return _Lib(C.CDLL(LIB_PATH))
 
 
 lib = _load()

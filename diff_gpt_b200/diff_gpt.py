@@ -1,0 +1,173 @@
+"""`DiffGPT` forecasting facade over the device engine.
+
+Keeps the reference's inference surface (src/diff_gpt/diff_gpt.py:15-37,127-293,365-505):
+`predict` (autoregressive and teacher-forced), `predict_samples`, `predict_quantiles`,
+`save`, `load`, with the same assertions and return types.  Differences are internal:
+the Monte-Carlo trajectories come from one device-resident decode, and all
+trajectories are turned back into values by one vectorised integration instead of a
+Python loop over samples (diff_gpt.py:239-252).
+
+Training (`train`, `train_numa`) and `anomaly_scores` belong to other parts of the
+reference and are not provided here.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import pandas as pd
+import torch
+
+from .encoder_decoder import decode, encode
+from .model.engine import Engine
+from .model.gpt import BaseGPT
+from .sampler.sampler import Sampler
+
+
+class DiffGPT:
+    __slots__ = ("model", "order_of_derivative", "domain_of_definition", "use_decimal")
+
+    def __init__(self, model: BaseGPT, order_of_derivative, domain_of_definition: np.ndarray, use_decimal: bool) -> None:
+        self.model = model
+        self.order_of_derivative = order_of_derivative
+        self.domain_of_definition = domain_of_definition
+        self.use_decimal = use_decimal
+
+    # ---- helpers ---------------------------------------------------------------------
+    def _max_order(self, n_cols: int, label: str) -> int:
+        order = self.order_of_derivative
+        if isinstance(order, (int, np.integer)):
+            return int(order)
+        arr = np.asarray(order)
+        assert arr.shape == (n_cols,), f"order_of_derivative shape {arr.shape} must match {label} {n_cols}"
+        return int(arr.max())
+
+    def _encode(self, values: np.ndarray):
+        return encode(
+            inp=values,
+            vocab_size=self.model.vocab_size,
+            domain_of_definition=self.domain_of_definition,
+            order_of_derivative=self.order_of_derivative,
+            use_decimal=self.use_decimal,
+        )
+
+    def _decode(self, start, scale, tokens: np.ndarray) -> np.ndarray:
+        return decode(
+            start=start,
+            scale=scale,
+            inp=tokens,
+            vocab_size=self.model.vocab_size,
+            order_of_derivative=self.order_of_derivative,
+            use_decimal=self.use_decimal,
+        )
+
+    # ---- Monte-Carlo futures ---------------------------------------------------------
+    def _generate_future_samples(self, df: pd.DataFrame, max_new_points: int, sampler: Sampler | None, num_samples: int) -> np.ndarray:
+        """(num_samples, max_new_points, n_features) float64: the forecast rows only."""
+        assert num_samples >= 1
+        rows, columns = df.shape
+        max_order = self._max_order(columns, "columns")
+        assert max_order <= rows, (
+            f"max order {max_order} > context length {rows}: "
+            f"not enough history to compute the k-th derivative prefix"
+        )
+        total_positions = (rows + max_new_points - max_order) * columns
+        assert total_positions <= self.model.block_size, (
+            f"prompt rows ({rows}) + new points ({max_new_points}) with "
+            f"{columns} columns (max_order={max_order}) require {total_positions} "
+            f"context positions, but block_size is {self.model.block_size}"
+        )
+        start, scale, encoded = self._encode(df.to_numpy(dtype=np.float64))
+        prompt = encoded.reshape(-1).astype(np.int64).tolist()  # row-major: (time, channel)
+        results, _ = Engine(model=self.model).generate_batch(
+            tokens=prompt, num_samples=num_samples, max_tokens=max_new_points * columns, sampler=sampler
+        )
+        tokens = np.asarray(results, dtype=np.int64).reshape(num_samples, -1, columns)
+        values = self._decode(start, scale, tokens)  # (N, rows + new, F), all trajectories at once
+        return np.ascontiguousarray(values[:, rows : rows + max_new_points, :])
+
+    @torch.inference_mode()
+    def predict_samples(self, df: pd.DataFrame, max_new_points: int, num_samples: int, sampler: Sampler | None = None) -> np.ndarray:
+        return self._generate_future_samples(df=df, max_new_points=max_new_points, sampler=sampler, num_samples=num_samples)
+
+    @torch.inference_mode()
+    def predict_quantiles(
+        self,
+        df: pd.DataFrame,
+        max_new_points: int,
+        quantiles=(0.1, 0.5, 0.9),
+        num_samples: int = 100,
+        sampler: Sampler | None = None,
+    ) -> dict[float, pd.DataFrame]:
+        for q in quantiles:
+            assert 0.0 < q < 1.0, f"quantile {q} must be in (0, 1)"
+        futures = self._generate_future_samples(df=df, max_new_points=max_new_points, sampler=sampler, num_samples=num_samples)
+        return {float(q): pd.DataFrame(np.quantile(futures, q, axis=0), columns=df.columns) for q in quantiles}
+
+    # ---- point forecasts ---------------------------------------------------------------
+    @torch.inference_mode()
+    def predict(
+        self,
+        df: pd.DataFrame,
+        max_new_points: int | None = None,
+        future_covariates_df: pd.DataFrame | None = None,
+        target_columns=None,
+        sampler: Sampler | None = None,
+    ) -> pd.DataFrame:
+        if future_covariates_df is None:
+            assert target_columns is None, "target_columns is only meaningful with future_covariates_df"
+            assert max_new_points is not None, "max_new_points is required when future_covariates_df is None"
+            future = self._generate_future_samples(df=df, max_new_points=max_new_points, sampler=sampler, num_samples=1)[0]
+            return pd.DataFrame(np.concatenate([df.to_numpy(dtype=np.float64), future], axis=0), columns=df.columns)
+        assert target_columns is not None and len(target_columns) > 0, (
+            "target_columns must be non-empty when future_covariates_df is given"
+        )
+        pred_len = len(future_covariates_df)
+        assert max_new_points is None or max_new_points == pred_len, (
+            f"max_new_points ({max_new_points}) must equal len(future_covariates_df) ({pred_len})"
+        )
+        return self._predict_teacher_forced(df, future_covariates_df, target_columns, sampler)
+
+    def _predict_teacher_forced(self, context_df, future_covariates_df, target_columns, sampler) -> pd.DataFrame:
+        """Known future columns are forced token by token, target columns are sampled (diff_gpt.py:396-498)."""
+        names = list(context_df.columns)
+        assert list(future_covariates_df.columns) == names, "context and future must have the same columns"
+        n_features = len(names)
+        targets: set[int] = set()
+        for c in target_columns:
+            if isinstance(c, str):
+                assert c in names, f"target column {c!r} not found in {names}"
+                targets.add(names.index(c))
+            else:
+                targets.add(int(c))
+        ctx_len, pred_len = len(context_df), len(future_covariates_df)
+        max_order = self._max_order(n_features, "n_features")
+        assert max_order <= ctx_len, (
+            f"max order {max_order} > context length {ctx_len}: "
+            f"not enough history to compute the k-th derivative prefix"
+        )
+        total_tokens = (ctx_len + pred_len - max_order) * n_features
+        assert total_tokens <= self.model.block_size, (
+            f"ctx={ctx_len} pred={pred_len} cols={n_features} (max_order={max_order}) "
+            f"need {total_tokens} tokens but block_size={self.model.block_size}"
+        )
+        frame = pd.concat([context_df, future_covariates_df], ignore_index=True).copy()
+        for c in targets:
+            frame.iloc[ctx_len:, c] = 0.0  # placeholders; these positions are generated
+        start, scale, encoded = self._encode(frame.to_numpy(dtype=np.float64))
+        flat = encoded.reshape(-1).astype(np.int64)
+        n_prompt = (ctx_len - max_order) * n_features
+        schedule = [None if (p % n_features) in targets else int(flat[p]) for p in range(n_prompt, total_tokens)]
+        results, _ = Engine(model=self.model).generate_batch(
+            tokens=flat[:n_prompt].tolist(), num_samples=1, max_tokens=total_tokens - n_prompt, sampler=sampler,
+            force_schedule=schedule,
+        )
+        tokens = np.asarray(results[0], dtype=np.int64).reshape(-1, n_features)
+        return pd.DataFrame(self._decode(start, scale, tokens), columns=names)
+
+    # ---- checkpoints --------------------------------------------------------------------
+    def save(self, path: str = "diff-gpt.bin") -> None:
+        torch.save(self.model.state_dict(), path)
+
+    def load(self, path: str = "diff-gpt.bin") -> None:
+        self.model.load_state_dict(torch.load(path, weights_only=True))
+        self.model.eval()

@@ -24,7 +24,7 @@ from typing import Callable, Generator
 
 import torch
 
-from .. import ops
+from .. import _lib, ops
 from ..sampler.sampler import Sampler
 from .gpt import GPT, BaseGPT, ForwardPlan, KvBinding, _pick_splits
 from .kv_cache import KVCache, PagedKVCache
@@ -74,7 +74,8 @@ class DecodeRun:
         self.temperature, self.top_p = spec if spec is not None else (1.0, 1.0)
         self.sampler = sampler
 
-        lens = [len(p) for p in prompts]
+        device_prompts = prompts if isinstance(prompts, torch.Tensor) else None  # [S, P] int32, already on the GPU
+        lens = [int(device_prompts.shape[1])] * S if device_prompts is not None else [len(p) for p in prompts]
         self.prompt_lens = lens
         self.cache = PagedKVCache(L, H, D, S, N, max(lens), G, dt, dev, page_tokens=page_tokens)
         self.prefix_lens = torch.tensor(lens, dtype=torch.int32, device=dev)
@@ -108,7 +109,10 @@ class DecodeRun:
                 fmha_impl=fmha_impl,
             )
             plan = ForwardPlan(model, len(members), P, last_only=True)
-            ids32 = torch.tensor([prompts[s] for s in members], dtype=torch.int32).reshape(-1).to(dev)
+            if device_prompts is not None:
+                ids32 = device_prompts.reshape(-1)
+            else:
+                ids32 = torch.tensor([prompts[s] for s in members], dtype=torch.int32).reshape(-1).to(dev)
             out = plan.run(ids32, bind)
             self.logits0[torch.tensor(members, device=dev)] = out
             self._keep = (table, layouts)  # keep the table alive until the work has been enqueued and run
@@ -210,12 +214,16 @@ class DecodeRun:
             ops.step_advance(self.step, 0)
             torch.cuda.synchronize(self.dev)
             self.graph = torch.cuda.CUDAGraph()
+            before = _lib.stats.launches
             with torch.cuda.graph(self.graph):
                 self._body()
             # capture does not execute: nothing has advanced yet
+            self.graph_launches = _lib.stats.launches - before
+            _lib.stats.launches = before
         for _ in range(n_steps):
             if self.graph is not None:
                 self.graph.replay()
+                _lib.stats.launches += self.graph_launches
             else:
                 self._body()
         self.done += n_steps

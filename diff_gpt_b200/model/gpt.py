@@ -27,6 +27,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .. import ops
+from .._lib import region
 from ..sampler.sampler import Sampler
 from .kv_cache import KVCache, PagedKVCache
 from .rope import precompute_freqs_cis
@@ -196,7 +197,8 @@ class ForwardPlan:
             if (i + 1) % m.attn_res_layers_per_block == 0:
                 cands = cands + [partial]
                 partial = None
-            torch.mm(self.u, lw.wqkvg_t, out=self.qkvg)
+            with region("gemm_qkvg"):
+                torch.mm(self.u, lw.wqkvg_t, out=self.qkvg)
             qv, kv_, vv, gv = (self.qkvg[:, j * C : (j + 1) * C] for j in range(4))
             ops.rope_qknorm_kvappend(
                 qv, kv_, vv, self.q, W.freqs_cis, b.layouts[i], b.pos0, b.slot0, b.step, n_seq, T, H, D, self.status
@@ -223,15 +225,18 @@ class ForwardPlan:
                 )
                 ops.sigmoid_gate(self.y, gv)
             part = self.parts[i]
-            if partial is None:
-                torch.mm(self.y, lw.wproj_t, out=part)
-            else:  # layers_per_block > 1: the running block sum keeps accumulating
-                torch.addmm(partial, self.y, lw.wproj_t, out=part)
+            with region("gemm_proj"):
+                if partial is None:
+                    torch.mm(self.y, lw.wproj_t, out=part)
+                else:  # layers_per_block > 1: the running block sum keeps accumulating
+                    torch.addmm(partial, self.y, lw.wproj_t, out=part)
             partial = part
             ops.depthmix(cands + [partial], lw.w_mlp, None, self.u)
-            torch.mm(self.u, lw.w1_t, out=self.f)
+            with region("gemm_ffn1"):
+                torch.mm(self.u, lw.w1_t, out=self.f)
             ops.swiglu(self.f, self.act, m.swiglu_alpha, m.swiglu_limit)
-            partial.addmm_(self.act, lw.w2_t)
+            with region("gemm_ffn2"):
+                partial.addmm_(self.act, lw.w2_t)
         final = partial
         if self.last is not None:
             self.last.copy_(partial.view(n_seq, T, C)[:, T - 1, :])
@@ -239,7 +244,8 @@ class ForwardPlan:
         ops.depthmix([final], None, None, self.xn)
         if self.logits is None:
             return None
-        torch.mm(self.xn, W.emb.t(), out=self.logits)
+        with region("gemm_logits"):
+            torch.mm(self.xn, W.emb.t(), out=self.logits)
         return self.logits
 
 

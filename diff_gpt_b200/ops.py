@@ -57,6 +57,7 @@ def kv_layout(
     lay.page_table = _ptr(page_table)
     lay.page_tokens = page_tokens
     lay.max_pages = 0 if page_table is None else page_table.shape[-1]
+    lay._keep = (k, v, page_table)  # the struct holds raw addresses: keep their owners alive with it
     return lay
 
 

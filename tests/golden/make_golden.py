@@ -201,6 +201,69 @@ def engine_force(ref):
     )
 
 
+def _series(rng, rows, cols):
+    t = np.arange(rows)[:, None]
+    periods = rng.integers(12, 169, size=(3, cols))
+    amps = rng.uniform(0.5, 2.0, size=(3, cols))
+    x = sum(amps[i] * np.sin(2 * np.pi * t / periods[i]) for i in range(3))
+    noise = np.zeros((rows, cols))
+    e = rng.normal(0, 0.1, size=(rows, cols))
+    for i in range(1, rows):
+        noise[i] = 0.8 * noise[i - 1] + e[i]
+    return (x + noise).astype(np.float64)
+
+
+def codec(ref):
+    """Tokeniser round trips: scalar orders 0..3, per-column orders, a vocabulary too small for MASH."""
+    from diff_gpt.encoder_decoder import decode, encode, get_domain_of_definition
+
+    rng = np.random.default_rng(21)
+    out = {}
+    cases = [("k0", 0, 256, 3), ("k1", 1, 256, 3), ("k2", 2, 256, 3), ("k3", 3, 256, 2), ("k2_v6", 2, 6, 2),
+             ("mixed", np.array([0, 1, 1, 2, 2, 1, 0]), 1024, 7)]
+    for tag, order, V, cols in cases:
+        x = _series(rng, 60, cols) if tag == "mixed" else np.cumsum(rng.normal(0, 1, (40, cols)), axis=0)
+        dom = get_domain_of_definition(x, order, use_decimal=False)
+        start, scale, tok = encode(inp=x, vocab_size=V, domain_of_definition=dom, order_of_derivative=order, use_decimal=False)
+        dec = decode(start=start, scale=scale, inp=tok, vocab_size=V, order_of_derivative=order, use_decimal=False)
+        out[f"{tag}:x"], out[f"{tag}:dom"], out[f"{tag}:start"] = x, np.asarray(dom, dtype=np.float64), np.asarray(start, dtype=np.float64)
+        out[f"{tag}:scale"], out[f"{tag}:tok"], out[f"{tag}:dec"] = np.asarray(scale, dtype=np.float64), tok, np.asarray(dec, dtype=np.float64)
+        out[f"{tag}:order"] = np.asarray(order, dtype=np.int64)
+        out[f"{tag}:V"] = np.asarray(V, dtype=np.int64)
+    np.savez_compressed(os.path.join(HERE, "codec.npz"), **out)
+
+
+def teacher_forced(ref):
+    """DiffGPT.predict with future covariates (3 channels, orders [0,1,2], channel 0 is the target) and
+    predict_samples / predict on the same tiny fp32 model, all under argmax."""
+    from diff_gpt.diff_gpt import DiffGPT
+    from diff_gpt.encoder_decoder import get_domain_of_definition
+    from diff_gpt.model.gpt import GPT
+    from diff_gpt.sampler.temperature import TemperatureSampler
+    import pandas as pd
+
+    V, C, H, L, block = 64, 32, 4, 2, 96
+    m = GPT(vocab_size=V, n_embd=C, block_size=block, n_head=H, n_layer=L).eval()
+    _init(m, 9, 0.3)
+    rng = np.random.default_rng(33)
+    x = _series(rng, 26, 3)
+    order = np.array([0, 1, 2])
+    dom = get_domain_of_definition(x, order, use_decimal=False)
+    dg = DiffGPT(model=m, order_of_derivative=order, domain_of_definition=dom, use_decimal=False)
+    ctx = pd.DataFrame(x[:20], columns=["a", "b", "c"])
+    fut = pd.DataFrame(x[20:], columns=["a", "b", "c"])
+    tf = dg.predict(ctx, future_covariates_df=fut, target_columns=["a"], sampler=TemperatureSampler(0.0))
+    ar = dg.predict(ctx, max_new_points=6, sampler=TemperatureSampler(0.0))
+    ps = dg.predict_samples(ctx, max_new_points=6, num_samples=3, sampler=TemperatureSampler(0.0))
+    np.savez_compressed(
+        os.path.join(HERE, "teacher_forced.npz"),
+        meta=np.array([V, C, H, L, block], dtype=np.int64),
+        x=x, order=order, dom=np.asarray(dom, dtype=np.float64),
+        teacher_forced=tf.to_numpy(), autoregressive=ar.to_numpy(), samples=ps,
+        **_weights(m),
+    )
+
+
 def main():
     ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     sys.path.insert(0, os.path.join(ref, "src"))
@@ -211,11 +274,13 @@ def main():
 
     small_forward(GPT, KVCache, "small_fp32", torch.float32, 64, 32, 4, 3, 16, 0.3, 0, 2, 9)
     small_forward(GPT, KVCache, "small_bf16_d64", torch.bfloat16, 128, 128, 2, 2, 32, 0.08, 1, 2, 13)
-    small_forward(GPT, KVCache, "small_bf16_d32", torch.bfloat16, 64, 64, 2, 3, 24, 0.15, 2, 3, 11)
+    small_forward(GPT, KVCache, "small_bf16_d32", torch.bfloat16, 64, 64, 2, 3, 24, 0.1, 2, 3, 11)
     config1(ref)
     samplers(ref)
     ops(ref)
     engine_force(ref)
+    codec(ref)
+    teacher_forced(ref)
 
 
 if __name__ == "__main__":

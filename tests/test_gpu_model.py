@@ -293,6 +293,43 @@ def test_samplers_standalone_contract():
     assert torch.isfinite(inner.lg).cpu().tolist() == [[True, True, True, False]]
 
 
+def test_diffgpt_facade_config1_and_teacher_forced():
+    """predict / predict_samples / predict_quantiles / teacher-forced predict reproduce the reference's
+    frames under argmax (values are decoded from identical token streams, so they match to the bit)."""
+    import pandas as pd
+
+    from diff_gpt_b200 import TemperatureSampler
+    from diff_gpt_b200.diff_gpt import DiffGPT
+
+    g = load_golden("cfg1_fp32")
+    m = _model(g["meta"], golden_weights(g, torch.float32), torch.float32)
+    dg = DiffGPT(model=m, order_of_derivative=1, domain_of_definition=g["domain"], use_decimal=False)
+    df = pd.DataFrame(g["ctx"], columns=["y"])
+    fut = dg.predict_samples(df, max_new_points=48, num_samples=4, sampler=TemperatureSampler(0.0))
+    assert fut.shape == (4, 48, 1) and np.array_equal(fut, g["futures_t0"])
+    pred = dg.predict(df, max_new_points=48, sampler=TemperatureSampler(0.0))
+    assert list(pred.columns) == ["y"] and np.array_equal(pred.to_numpy(), g["predict_t0"])
+    q = dg.predict_quantiles(df, 48, quantiles=(0.1, 0.5, 0.9), num_samples=4, sampler=TemperatureSampler(0.0))
+    assert np.array_equal(q[0.5].to_numpy(), g["q50_t0"])
+    # stochastic bands are ordered (reference test_diff_gpt.py:295-317)
+    qs = dg.predict_quantiles(df, 48, quantiles=(0.1, 0.5, 0.9), num_samples=64, sampler=TemperatureSampler(1.0))
+    assert (qs[0.1].to_numpy() <= qs[0.5].to_numpy()).all() and (qs[0.5].to_numpy() <= qs[0.9].to_numpy()).all()
+    with pytest.raises(AssertionError, match="block_size"):
+        dg.predict_samples(pd.DataFrame(g["walk"].reshape(-1, 1), columns=["y"]), 48, 2)  # 96 + 48 - 1 > 138
+
+    t = load_golden("teacher_forced")
+    m2 = _model(t["meta"], golden_weights(t, torch.float32), torch.float32)
+    dg2 = DiffGPT(model=m2, order_of_derivative=t["order"], domain_of_definition=t["dom"], use_decimal=False)
+    ctx = pd.DataFrame(t["x"][:20], columns=["a", "b", "c"])
+    future = pd.DataFrame(t["x"][20:], columns=["a", "b", "c"])
+    tf = dg2.predict(ctx, future_covariates_df=future, target_columns=["a"], sampler=TemperatureSampler(0.0))
+    assert np.array_equal(tf.to_numpy(), t["teacher_forced"])
+    ar = dg2.predict(ctx, max_new_points=6, sampler=TemperatureSampler(0.0))
+    assert np.array_equal(ar.to_numpy(), t["autoregressive"])
+    ps = dg2.predict_samples(ctx, max_new_points=6, num_samples=3, sampler=TemperatureSampler(0.0))
+    assert np.array_equal(ps, t["samples"])
+
+
 def test_kv_cache_reference_surface():
     """Lazy allocation, growth in multiples of 1024, pos on the last layer only, batch broadcast, reset
     (reference tests/diff_gpt/model/test_kv_cache.py)."""
