@@ -34,6 +34,7 @@ class KvLayout(C.Structure):
         ("page_table", C.c_void_p),
         ("page_tokens", C.c_int32),
         ("max_pages", C.c_int32),
+        ("n_pages", C.c_int64),
     ]
 
 

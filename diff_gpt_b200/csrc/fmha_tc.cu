@@ -1,13 +1,531 @@
-// tcgen05 / TMEM prefill attention (bf16, head_dim 64 or 128).
+// tcgen05 / TMEM prefill attention for bf16, head_dim 64 or 128 (sm_100a).
+//
+// One CTA of 128 threads owns a 128-query tile of one (batch, head); thread t owns
+// query row t, which is also TMEM lane t.  Per 128-key tile:
+//   TMA     Q once, K and V tiles (128-byte swizzled, one box per page and per 64-wide half of D)
+//   UMMA 1  S = Q K^T          -> TMEM columns [0,128) fp32           (tcgen05.mma, operands in smem)
+//   softmax rows read S with tcgen05.ld, exponentiate, write P as packed bf16 over S (tcgen05.st)
+//   UMMA 2  O_tile = P V       -> TMEM columns [128,128+D) fp32       (A = P from TMEM, B = V MN-major)
+//   rows add O_tile into fp32 register accumulators with the usual online-softmax rescale.
+// Two CTAs are resident per SM (256 TMEM columns and <= 97 KB of shared memory each), so one
+// CTA's softmax overlaps the other's tensor-core work.  No cluster launch and no multicast.
+// Every wait on an mbarrier is bounded; if one runs out the CTA records a status word, drains
+// what it issued, frees its TMEM and returns.
+#include <cuda.h>
+
 #include "fmha.cuh"
 
 namespace dgpt {
+namespace tc {
 
-bool fmha_tc_supported(const FmhaArgs&, const dgpt_kv_layout&) { return false; }
+constexpr int kBM = 128;          // queries per CTA
+constexpr int kBN = 128;          // keys per tile
+constexpr int kTmemCols = 256;    // S/P: [0,128), O tile: [128, 128 + D)
+constexpr uint32_t kSpinLimit = 1u << 24;
 
-int fmha_tc(const FmhaArgs&, const dgpt_kv_layout&, cudaStream_t) {
-  set_error("fmha_tc: not built");
-  return DGPT_E_UNSUPPORTED;
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false if the phase did not complete within kSpinLimit polls.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
+                                            int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr)
+      : "memory");
+  tc_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// 16 consecutive 32-bit columns (32 packed bf16) of this thread's TMEM lane
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
+// lbo/sbo in bytes.  K-major operands ignore lbo; MN-major use lbo between 64-element blocks.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: bf16 x bf16 -> fp32, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(kBM >> 4) << 24);
+}
+
+struct Params {
+  const int* kv_len;
+  int kv_len_all;
+  const int* page_table;
+  int max_pages;
+  int page_tokens;
+  void* o;
+  long long o_bs, o_rs;
+  int o_f32;
+  float* lse;
+  int H, Tq, q_offset, causal;
+  float scale_log2;
+  int* status;
+};
+
+// Bounded wait that also gives up early when another thread has raised the CTA's abort flag.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+template <int D>
+__global__ void __launch_bounds__(128, 2)
+fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+               const __grid_constant__ CUtensorMap mv, const Params p) {
+  constexpr int kSub = D / 64;                  // 64-element (128-byte) column blocks per row
+  constexpr uint32_t kSubBytes = kBN * 128;     // one [128 rows][64 bf16] swizzled block
+  constexpr uint32_t kTileBytes = kSub * kSubBytes;
+  constexpr uint32_t kIdescS = instr_desc(kBN, false);
+  constexpr uint32_t kIdescPV = instr_desc(D, true);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + kTileBytes;
+  uint8_t* sV = smem + 2 * kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * kTileBytes);  // q, k, v, s, o
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar_q = smem_u32(bars), bar_k = bar_q + 8, bar_v = bar_q + 16, bar_s = bar_q + 24, bar_o = bar_q + 32;
+  const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int qt = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;  // long tiles first
+  const int q0 = qt * kBM;
+  const int klen = p.kv_len ? p.kv_len[b] : p.kv_len_all;
+  const int kmax = p.causal ? min(klen, p.q_offset + min(q0 + kBM, p.Tq)) : klen;
+  const int n_tiles = kmax > 0 ? (kmax + kBN - 1) / kBN : 0;
+  const int pt = p.page_tokens;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_q, 1);
+    mbar_init(bar_k, 1);
+    mbar_init(bar_v, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+
+  // Issue the TMA loads of key/value tile j (thread 0 only).  One box per page and per 64-wide half.
+  auto load_kv = [&](const CUtensorMap* map, uint32_t dst, uint32_t bar, int j) {
+    const int t0 = j * kBN;
+    if (pt >= kBN) {
+      const int lp = t0 / pt, in = t0 - lp * pt;
+      const int pg = p.page_table ? p.page_table[(long long)b * p.max_pages + lp] : b;
+      mbar_expect_tx(bar, kTileBytes);
+#pragma unroll
+      for (int s = 0; s < kSub; ++s) tma_load_4d(dst + s * kSubBytes, map, bar, s * 64, in, h, pg);
+    } else {
+      const int per = kBN / pt;
+      int valid = 0;
+      for (int q = 0; q < per; ++q) valid += (t0 + q * pt < klen) ? 1 : 0;
+      mbar_expect_tx(bar, (uint32_t)valid * pt * 128u * kSub);
+      for (int q = 0; q < valid; ++q) {
+        const int lp = t0 / pt + q;
+        const int pg = p.page_table ? p.page_table[(long long)b * p.max_pages + lp] : b;
+#pragma unroll
+        for (int s = 0; s < kSub; ++s) tma_load_4d(dst + s * kSubBytes + q * pt * 128, map, bar, s * 64, 0, h, pg);
+      }
+    }
+  };
+
+  float acc[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) acc[d] = 0.f;
+  float m = -INFINITY, l = 0.f;
+  bool fail = false;
+  int pend_k = -1, pend_v = -1, pend_s = -1, pend_o = -1;  // thread 0: parity of an outstanding phase, or -1
+
+  if (tid == 0 && n_tiles > 0) {
+    mbar_expect_tx(bar_q, kTileBytes);
+#pragma unroll
+    for (int s = 0; s < kSub; ++s) tma_load_4d(aQ + s * kSubBytes, &mq, bar_q, s * 64, h, q0, b);
+    load_kv(&mk, aK, bar_k, 0);
+    load_kv(&mv, aV, bar_v, 0);
+    pend_k = pend_v = 0;
+  }
+
+  for (int j = 0; j < n_tiles; ++j) {
+    const uint32_t par = (uint32_t)(j & 1);
+    const int t0 = j * kBN;
+    // ---- S = Q K^T ----
+    if (tid == 0) {
+      bool ok = true;
+      if (j == 0) ok = wait_or_abort(bar_q, 0, abort_flag);
+      ok = ok && wait_or_abort(bar_k, par, abort_flag);
+      if (ok) {
+        pend_k = -1;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (uint32_t)(ks >> 2) * kSubBytes + (uint32_t)(ks & 3) * 32u;
+          umma_ss(tmem, smem_desc(aQ + off, 16, 1024), smem_desc(aK + off, 16, 1024), kIdescS, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(bar_s);
+        pend_s = (int)par;
+      } else {
+        fail = true;
+      }
+    }
+    if (!wait_or_abort(bar_s, par, abort_flag)) fail = true;
+    if (!wait_or_abort(bar_v, par, abort_flag)) fail = true;
+    tc_fence_after();
+    if (tid == 0 && !fail) {
+      pend_s = -1;
+      pend_v = -1;
+      if (j + 1 < n_tiles) {
+        load_kv(&mk, aK, bar_k, j + 1);  // the K buffer is free once S has been produced
+        pend_k = (int)(par ^ 1u);
+      }
+    }
+    // value rows past the end of the sequence may hold anything: clear them so that 0 * x stays 0
+    const int valid_rows = klen - t0;
+    if (valid_rows < kBN && tid >= valid_rows) {
+#pragma unroll
+      for (int s = 0; s < kSub; ++s) {
+        uint4* row = reinterpret_cast<uint4*>(sV + s * kSubBytes + tid * 128);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) row[c] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      fence_async_smem();
+    }
+    // ---- softmax of this row ----
+    const bool need_mask = (t0 + kBN > klen) || (p.causal && t0 + kBN - 1 > p.q_offset + q0);
+    const int last_key = p.causal ? min(klen - 1, p.q_offset + q0 + tid) : klen - 1;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float v[32];
+      tmem_ld32(lane_addr + c * 32, v);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const bool vis = !need_mask || (t0 + c * 32 + i <= last_key);
+        mx = fmaxf(mx, vis ? v[i] : -INFINITY);
+      }
+    }
+    const float m_new = fmaxf(m, mx * p.scale_log2);
+    const float alpha = (m == -INFINITY) ? 0.f : ex2(m - m_new);
+    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+    float rowsum = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float v[32];
+      tmem_ld32(lane_addr + c * 32, v);
+      uint32_t packed[16];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        const bool v0 = !need_mask || (t0 + c * 32 + i <= last_key);
+        const bool v1 = !need_mask || (t0 + c * 32 + i + 1 <= last_key);
+        const float p0 = v0 ? ex2(v[i] * p.scale_log2 - m_use) : 0.f;
+        const float p1 = v1 ? ex2(v[i + 1] * p.scale_log2 - m_use) : 0.f;
+        rowsum += p0 + p1;
+        const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+        packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+      }
+      tmem_st16(lane_addr + c * 16, packed);  // P overwrites the part of S this row has already consumed
+    }
+    l = l * alpha + rowsum;
+    m = m_new;
+    tc_wait_st();
+    tc_fence_before();
+    if (__syncthreads_or(fail ? 1 : 0)) {
+      fail = true;
+      break;
+    }
+    // ---- O_tile = P V ----
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < kBN / 16; ++ks)
+        umma_ts(tmem + 128, tmem + ks * 8, smem_desc(aV + ks * 2048, kSubBytes, 1024), kIdescPV, ks > 0 ? 1u : 0u);
+      umma_commit(bar_o);
+      pend_o = (int)par;
+    }
+#pragma unroll
+    for (int d = 0; d < D; ++d) acc[d] *= alpha;
+    if (!wait_or_abort(bar_o, par, abort_flag)) fail = true;
+    tc_fence_after();
+    if (tid == 0 && !fail) {
+      pend_o = -1;
+      if (j + 1 < n_tiles) {
+        load_kv(&mv, aV, bar_v, j + 1);
+        pend_v = (int)(par ^ 1u);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) {
+      float v[32];
+      tmem_ld32(lane_addr + 128 + c * 32, v);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) acc[c * 32 + i] += v[i];
+    }
+    tc_fence_before();
+    if (__syncthreads_or(fail ? 1 : 0)) {
+      fail = true;
+      break;
+    }
+  }
+
+  if (!fail) {
+    const int qi = q0 + tid;
+    if (qi < p.Tq) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const long long off = (long long)b * p.o_bs + (long long)qi * p.o_rs + (long long)h * D;
+      if (p.o_f32) {
+        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.o) + off);
+#pragma unroll
+        for (int d = 0; d < D; d += 4)
+          dst[d >> 2] = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
+      } else {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.o) + off);
+#pragma unroll
+        for (int d = 0; d < D; d += 8) {
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[d] * inv, acc[d + 1] * inv);
+          __nv_bfloat162 h1 = __floats2bfloat162_rn(acc[d + 2] * inv, acc[d + 3] * inv);
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[d + 4] * inv, acc[d + 5] * inv);
+          __nv_bfloat162 h3 = __floats2bfloat162_rn(acc[d + 6] * inv, acc[d + 7] * inv);
+          dst[d >> 3] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                                   *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+        }
+      }
+      if (p.lse) p.lse[((long long)b * p.Tq + qi) * p.H + h] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
+    }
+  } else if (tid == 0) {
+    // a wait ran out: record it, then give whatever is still in flight a bounded chance to land
+    if (p.status) atomicExch(p.status, 2);
+    if (pend_k >= 0) mbar_wait(bar_k, (uint32_t)pend_k);
+    if (pend_v >= 0) mbar_wait(bar_v, (uint32_t)pend_v);
+    if (pend_s >= 0) mbar_wait(bar_s, (uint32_t)pend_s);
+    if (pend_o >= 0) mbar_wait(bar_o, (uint32_t)pend_o);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+// ---- host side -------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn encode_fn() {
+  static EncodeFn fn = []() -> EncodeFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+static bool device_is_sm100() {
+  static int major = []() {
+    int dev = 0, mj = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    cudaDeviceGetAttribute(&mj, cudaDevAttrComputeCapabilityMajor, dev);
+    return mj;
+  }();
+  return major == 10;
+}
+
+// 4-D bf16 tensor map with a [rows][64] box, 128-byte swizzle; dim 0 is the head dimension.
+static bool encode_map(CUtensorMap* map, const void* base, const cuuint64_t (&dims)[4], const cuuint64_t (&strides)[3],
+                       const cuuint32_t (&box)[4]) {
+  const cuuint32_t ones[4] = {1, 1, 1, 1};
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, ones,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("fmha_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return false;
+  }
+  return true;
+}
+
+}  // namespace tc
+
+bool fmha_tc_supported(const FmhaArgs& a, const dgpt_kv_layout& kv) {
+  if (a.dtype != DGPT_BF16 || (a.D != 64 && a.D != 128)) return false;
+  const int pt = kv.page_tokens;
+  if (!((pt >= tc::kBN && pt % tc::kBN == 0) || (pt >= 8 && pt < tc::kBN && tc::kBN % pt == 0))) return false;
+  if (kv.page_table == nullptr && pt < tc::kBN) return false;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (!al16(a.q) || !al16(a.o) || !al16(kv.k_base) || !al16(kv.v_base)) return false;
+  if (a.q_rs % 8 || a.q_bs % 8 || a.o_rs % 8 || a.o_bs % 8 || kv.head_stride % 8 || kv.page_stride % 8) return false;
+  if (a.q_rs <= 0 || kv.head_stride <= 0 || kv.page_stride <= 0) return false;
+  return tc::device_is_sm100() && tc::encode_fn() != nullptr;
+}
+
+int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
+  using namespace tc;
+  const int D = a.D;
+  CUtensorMap mq, mk, mv;
+  {
+    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)a.H, (cuuint64_t)a.Tq, (cuuint64_t)a.B};
+    const cuuint64_t q_bs = a.q_bs > 0 ? (cuuint64_t)a.q_bs : (cuuint64_t)a.q_rs * a.Tq;
+    const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)a.q_rs * 2, q_bs * 2};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)kBM, 1};
+    if (!encode_map(&mq, a.q, dims, strides, box)) return DGPT_E_CUDA;
+  }
+  {
+    const int pt = kv.page_tokens;
+    cuuint64_t n_pages = kv.page_table ? (kv.n_pages > 0 ? (cuuint64_t)kv.n_pages : (cuuint64_t)1 << 24) : (cuuint64_t)a.B;
+    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)pt, (cuuint64_t)a.H, n_pages};
+    const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)kv.head_stride * 2, (cuuint64_t)kv.page_stride * 2};
+    const cuuint32_t box[4] = {64, (cuuint32_t)(pt < kBN ? pt : kBN), 1, 1};
+    if (!encode_map(&mk, kv.k_base, dims, strides, box)) return DGPT_E_CUDA;
+    if (!encode_map(&mv, kv.v_base, dims, strides, box)) return DGPT_E_CUDA;
+  }
+  Params p;
+  p.kv_len = a.kv_len;
+  p.kv_len_all = a.kv_len_all;
+  p.page_table = kv.page_table;
+  p.max_pages = kv.max_pages;
+  p.page_tokens = kv.page_tokens;
+  p.o = a.o;
+  p.o_bs = a.o_bs;
+  p.o_rs = a.o_rs;
+  p.o_f32 = a.o_f32;
+  p.lse = a.lse;
+  p.H = a.H;
+  p.Tq = a.Tq;
+  p.q_offset = a.q_offset;
+  p.causal = a.causal;
+  p.scale_log2 = kLog2e / sqrtf((float)D);
+  p.status = a.status;
+  dim3 grid((unsigned)((a.Tq + kBM - 1) / kBM), (unsigned)a.H, (unsigned)a.B);
+  // >= 80 KB per CTA keeps residency at two CTAs per SM, which is what the 2 x 256 TMEM columns allow
+  size_t smem = (size_t)3 * (D / 64) * kBN * 128 + 64 + 1024;
+  if (smem < 80 * 1024) smem = 80 * 1024;
+  cudaError_t e;
+  if (D == 64) {
+    e = cudaFuncSetAttribute(fmha_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) fmha_tc_kernel<64><<<grid, 128, smem, st>>>(mq, mk, mv, p);
+  } else {
+    e = cudaFuncSetAttribute(fmha_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) fmha_tc_kernel<128><<<grid, 128, smem, st>>>(mq, mk, mv, p);
+  }
+  if (e != cudaSuccess) {
+    set_error("fmha_tc: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    return DGPT_E_CUDA;
+  }
+  return launch_status("fmha_tc");
 }
 
 }  // namespace dgpt

@@ -143,7 +143,10 @@ class PagedKVCache:
     def _layout(self, layer: int, table: torch.Tensor) -> ops.KvLayout:
         H, pt, D = self.n_head, self.page_tokens, self.head_dim
         p = self.pool[layer]
-        return ops.kv_layout(p[0, 0], p[0, 1], page_stride=2 * H * pt * D, head_stride=pt * D, page_tokens=pt, page_table=table)
+        return ops.kv_layout(
+            p[0, 0], p[0, 1], page_stride=2 * H * pt * D, head_stride=pt * D, page_tokens=pt, page_table=table,
+            n_pages=p.shape[0],
+        )
 
     def prefix_layout(self, layer: int) -> ops.KvLayout:
         """Sequence index = series (prompt prefill and the shared-prefix attention phase)."""

@@ -46,10 +46,12 @@ def kv_layout(
     head_stride: int,
     page_tokens: int,
     page_table: torch.Tensor | None = None,
+    n_pages: int = 0,
 ) -> KvLayout:
     """Descriptor of one layer's K/V storage; `k`/`v` are views whose first element is the base."""
     _cuda(k, v, page_table)
     lay = KvLayout()
+    lay.n_pages = n_pages
     lay.k_base = k.data_ptr()
     lay.v_base = v.data_ptr()
     lay.page_stride = page_stride

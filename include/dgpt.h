@@ -53,6 +53,7 @@ typedef struct dgpt_kv_layout {
   const int32_t* page_table; /* device, [n_seq][max_pages], or NULL */
   int32_t page_tokens;
   int32_t max_pages;
+  int64_t n_pages;           /* pages addressable from the bases when a page table is used (0 = not stated) */
 } dgpt_kv_layout;
 
 /* Text of the last error raised on this host thread; returns its length. */

@@ -1,0 +1,81 @@
+"""tcgen05 prefill-attention kernel (bf16, head_dim 64/128) against the CPU oracle."""
+
+import math
+
+import pytest
+import torch
+
+from oracle import ref_math
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(D, B, H, Tq, Tk, pt, causal, q_offset, use_table, o_f32, impl=2, seed=0):
+    from diff_gpt_b200 import ops
+
+    gen = torch.Generator().manual_seed(seed + D + Tq)
+    dt = torch.bfloat16
+    cap = -(-max(Tk) // pt) * pt if use_table else pt
+    q = torch.randn(B, Tq, H, D, generator=gen).to(dt)
+    k = torch.randn(B, H, cap, D, generator=gen).to(dt)
+    v = torch.randn(B, H, cap, D, generator=gen).to(dt)
+    if use_table:
+        pages = cap // pt
+        perm = torch.randperm(B * pages, generator=gen).to(torch.int32).view(B, pages)
+        pool = torch.full((B * pages + 1, 2, H, pt, D), float("nan"), dtype=dt, device="cuda")
+        for b in range(B):
+            for p in range(pages):
+                pool[perm[b, p], 0] = k[b, :, p * pt : (p + 1) * pt].cuda()
+                pool[perm[b, p], 1] = v[b, :, p * pt : (p + 1) * pt].cuda()
+        lay = ops.kv_layout(pool[0, 0], pool[0, 1], 2 * H * pt * D, pt * D, pt, perm.cuda(), n_pages=pool.shape[0])
+    else:
+        pool = torch.stack([k, v], dim=1).cuda().contiguous()  # (B, 2, H, cap, D): one page per sequence
+        lay = ops.kv_layout(pool[0, 0], pool[0, 1], 2 * H * cap * D, cap * D, cap)
+    o = torch.full((B, Tq, H, D), float("nan"), dtype=torch.float32 if o_f32 else dt, device="cuda")
+    lse = torch.empty(B, Tq, H, dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.fmha_prefill(
+        q.cuda(), lay, o, B=B, H=H, Tq=Tq, D=D, q_batch_stride=Tq * H * D, q_row_stride=H * D,
+        o_batch_stride=Tq * H * D, o_row_stride=H * D, kv_len=torch.tensor(Tk, dtype=torch.int32, device="cuda"),
+        q_offset=q_offset, causal=causal, lse=lse, impl=impl, status=status,
+    )
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    for b in range(B):
+        qh = q[b : b + 1].transpose(1, 2)
+        kk, vv = k[b : b + 1, :, : Tk[b]], v[b : b + 1, :, : Tk[b]]
+        want = ref_math.sdpa(qh.float(), kk.float(), vv.float(), q_offset=q_offset if causal else 10**7).transpose(1, 2)
+        got = o[b : b + 1].float().cpu()
+        err = (got - want).abs().max().item() / want.abs().max().item()
+        assert err <= 1.5e-2, (b, err)
+        s = torch.matmul(qh.float(), kk.float().transpose(-1, -2)) / math.sqrt(D)
+        if causal:
+            i = torch.arange(Tq)[:, None]
+            j = torch.arange(Tk[b])[None, :]
+            s = s.masked_fill(j > q_offset + i, float("-inf"))
+        want_lse = torch.logsumexp(s, dim=-1).transpose(1, 2)
+        assert (lse[b : b + 1].cpu() - want_lse).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("D", [64, 128])
+def test_single_tile(D):
+    _run(D, B=1, H=1, Tq=128, Tk=[128], pt=128, causal=False, q_offset=0, use_table=False, o_f32=False)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_multi_tile_dense(D, causal):
+    _run(D, B=2, H=2, Tq=300, Tk=[384, 300] if not causal else [300, 300], pt=384, causal=causal, q_offset=0,
+         use_table=False, o_f32=False)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("pt", [16, 64, 128])
+def test_paged_ragged_offset(D, pt):
+    _run(D, B=2, H=3, Tq=37, Tk=[48, 43], pt=pt, causal=True, q_offset=11, use_table=True, o_f32=False)
+    _run(D, B=2, H=2, Tq=200, Tk=[700, 513], pt=pt, causal=False, q_offset=0, use_table=True, o_f32=True)
+
+
+def test_matches_warp_level_kernel_on_a_long_causal_case():
+    _run(128, B=1, H=2, Tq=1024, Tk=[1024], pt=1024, causal=True, q_offset=0, use_table=False, o_f32=False)
+    _run(64, B=1, H=2, Tq=640, Tk=[1024], pt=64, causal=True, q_offset=384, use_table=True, o_f32=False)
