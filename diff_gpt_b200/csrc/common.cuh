@@ -69,6 +69,46 @@ __device__ __forceinline__ void ld16<__nv_bfloat16>(const __nv_bfloat16* p, floa
   }
 }
 
+// 16-byte vector store of VEC fp32 values scaled by `s` and rounded to the storage type.
+template <typename T>
+__device__ __forceinline__ void st16(T* p, const float* v, float s);
+
+template <>
+__device__ __forceinline__ void st16<float>(float* p, const float* v, float s) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0] * s, v[1] * s, v[2] * s, v[3] * s);
+}
+
+template <>
+__device__ __forceinline__ void st16<__nv_bfloat16>(__nv_bfloat16* p, const float* v, float s) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i] * s, v[2 * i + 1] * s);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Widen the VEC elements held in one raw 16-byte register quad.
+template <typename T>
+__device__ __forceinline__ void unpack16(const uint4& v, float* out);
+
+template <>
+__device__ __forceinline__ void unpack16<float>(const uint4& v, float* out) {
+  out[0] = __uint_as_float(v.x); out[1] = __uint_as_float(v.y);
+  out[2] = __uint_as_float(v.z); out[3] = __uint_as_float(v.w);
+}
+
+template <>
+__device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4& v, float* out) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
 // ---- reductions -------------------------------------------------------------
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -72,39 +72,65 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
 
   const T* kbase = static_cast<const T*>(kv.k);
   const T* vbase = static_cast<const T*>(kv.v);
-  for (int i0 = begin; i0 < end; i0 += 2 * TPW) {  // warp-uniform trip count
-    float kf[2][VEC], vf[2][VEC];
-    bool ok[2];
+  constexpr int U = 4;  // 16-byte loads in flight per lane and per tensor
+  // Walk the keys page by page: one page-table lookup per page, then a dense run of tokens.
+  for (int i = begin; i < end;) {  // every quantity below is warp-uniform
+    const bool in0 = i < n0;
+    const int slot = in0 ? i : s1 + (i - n0);
+    const int lp = slot / kv.page_tokens;
+    const int in = slot - lp * kv.page_tokens;
+    const int cnt = min((in0 ? min(n0, end) : end) - i, kv.page_tokens - in);
+    const long long pg = kv.page_table ? (long long)kv.page_table[(long long)r * kv.max_pages + lp] : (long long)r;
+    const long long base = pg * kv.page_stride + (long long)h * kv.head_stride + (long long)in * D + e * VEC;
+    for (int t0 = 0; t0 < cnt; t0 += U * TPW) {
+      uint4 kr[U], vr[U];
+      bool ok[U];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int i = i0 + u * TPW + g;
-      ok[u] = i < end;
-      if (ok[u]) {
-        const int slot = i < n0 ? i : s1 + (i - n0);
-        const long long off = kv_offset(kv, r, h, slot, D) + e * VEC;
-        ld16<T>(kbase + off, kf[u]);
-        ld16<T>(vbase + off, vf[u]);
+      for (int u = 0; u < U; ++u) {
+        const int t = t0 + u * TPW + g;
+        ok[u] = t < cnt;
+        if (ok[u]) {
+          kr[u] = *reinterpret_cast<const uint4*>(kbase + base + (long long)t * D);
+          vr[u] = *reinterpret_cast<const uint4*>(vbase + base + (long long)t * D);
+        }
       }
-    }
+      float s[U];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      float s = 0.f;
-      if (ok[u]) {
+      for (int u = 0; u < U; ++u) {
+        float kf[VEC];
+        unpack16<T>(kr[u], kf);
+        float d = 0.f;
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) s += qf[i] * kf[u][i];
+        for (int x = 0; x < VEC; ++x) d += qf[x] * kf[x];
+        s[u] = ok[u] ? d : 0.f;
       }
 #pragma unroll
-      for (int o = LPT >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (ok[u]) {
-        const float mn = fmaxf(m, s);
+      for (int o = LPT >> 1; o > 0; o >>= 1) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) s[u] += __shfl_xor_sync(0xffffffffu, s[u], o);
+      }
+      if (ok[0]) {  // tokens of a lane group are valid in order, so ok[0] covers "any valid"
+        float mb = s[0];
+#pragma unroll
+        for (int u = 1; u < U; ++u) mb = ok[u] ? fmaxf(mb, s[u]) : mb;
+        const float mn = fmaxf(m, mb);
         const float resc = exp2f(m - mn);  // m = -inf -> 0
-        const float p = exp2f(s - mn);
-        l = l * resc + p;
+        l *= resc;
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) acc[i] = acc[i] * resc + p * vf[u][i];
+        for (int x = 0; x < VEC; ++x) acc[x] *= resc;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const float pw = ok[u] ? exp2f(s[u] - mn) : 0.f;
+          float vf[VEC];
+          unpack16<T>(vr[u], vf);
+          l += pw;
+#pragma unroll
+          for (int x = 0; x < VEC; ++x) acc[x] += pw * (ok[u] ? vf[x] : 0.f);
+        }
         m = mn;
       }
     }
+    i += cnt;
   }
   // merge the TPW lane groups (butterfly: every lane ends with the full state)
 #pragma unroll

@@ -126,11 +126,112 @@ __global__ void depthmix_kernel(CandPtrs cands, int n_cands, const T* __restrict
   }
 }
 
+// Same algorithm with 16-byte accesses: lane l owns vectors l + 32*i (i < NV) of VEC elements each.
+// Used when n_embd is a multiple of VEC and every pointer is 16-byte aligned.
+template <typename T, int NV>
+__global__ void depthmix_vec_kernel(CandPtrs cands, int n_cands, const T* __restrict__ w, T* __restrict__ out_h,
+                                    T* __restrict__ out_rn, long long rows, int C) {
+  constexpr int VEC = Io<T>::kVec16;
+  constexpr int E = NV * VEC;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int nvec = C / VEC;
+  float acc[E], wv[E];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int j = lane + 32 * i;
+#pragma unroll
+    for (int x = 0; x < VEC; ++x) acc[i * VEC + x] = wv[i * VEC + x] = 0.f;
+    if (n_cands > 1 && j < nvec) ld16<T>(w + j * VEC, wv + i * VEC);
+  }
+  float m = -INFINITY, l = 0.f;
+  // The candidates are reduced one after another (online softmax), so the next candidate's row is
+  // fetched (as raw 16-byte words) before the current one is reduced, to keep loads in flight.
+  uint4 nxt[NV];
+  auto fetch = [&](int n) {
+    const T* src = static_cast<const T*>(cands.p[n]) + row * C;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int j = lane + 32 * i;
+      nxt[i] = j < nvec ? *reinterpret_cast<const uint4*>(src + j * VEC) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  fetch(0);
+  for (int n = 0; n < n_cands; ++n) {
+    float v[E];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) unpack16<T>(nxt[i], v + i * VEC);
+    if (n + 1 < n_cands) fetch(n + 1);
+#pragma unroll
+    for (int x = 0; x < E; ++x) ss += v[x] * v[x];
+    if (n_cands == 1) {
+#pragma unroll
+      for (int x = 0; x < E; ++x) acc[x] = v[x];
+      l = 1.f;
+      break;
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)C + kRmsEps);
+    float dot = 0.f;
+#pragma unroll
+    for (int x = 0; x < E; ++x) dot += Io<T>::round(v[x] * inv) * wv[x];
+    dot = Io<T>::round(warp_sum(dot));
+    const float m_new = fmaxf(m, dot);
+    const float resc = __expf(m - m_new);
+    const float pw = __expf(dot - m_new);
+    l = l * resc + pw;
+#pragma unroll
+    for (int x = 0; x < E; ++x) acc[x] = acc[x] * resc + pw * v[x];
+    m = m_new;
+  }
+  const float invl = 1.f / l;
+  float ss = 0.f;
+#pragma unroll
+  for (int x = 0; x < E; ++x) {
+    acc[x] = Io<T>::round(acc[x] * invl);
+    ss += acc[x] * acc[x];
+  }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)C + kRmsEps);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int j = lane + 32 * i;
+    if (j >= nvec) continue;
+    if (out_h) st16<T>(out_h + row * C + j * VEC, acc + i * VEC, 1.f);
+    if (out_rn) st16<T>(out_rn + row * C + j * VEC, acc + i * VEC, inv);
+  }
+}
+
+template <typename T>
+static bool depthmix_vec_ok(const CandPtrs& cp, int n, const void* w, void* out_h, void* out_rn, int C) {
+  constexpr int VEC = Io<T>::kVec16;
+  if (C % VEC != 0 || C / VEC > 32 * 8) return false;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  for (int i = 0; i < n; ++i)
+    if (!al(cp.p[i])) return false;
+  return al(w) && al(out_h) && al(out_rn);
+}
+
 template <typename T>
 static int depthmix_launch(const CandPtrs& cp, int n, const void* w, void* out_h, void* out_rn,
                            long long rows, int C, cudaStream_t st) {
   const int warps = 4;
   const unsigned grid = (unsigned)((rows + warps - 1) / warps);
+  if (depthmix_vec_ok<T>(cp, n, w, out_h, out_rn, C)) {
+    const int nv = (C / Io<T>::kVec16 + 31) / 32;
+#define DGPT_MIXV(N)                                                                           \
+  depthmix_vec_kernel<T, N><<<grid, warps * 32, 0, st>>>(cp, n, static_cast<const T*>(w),      \
+                                                         static_cast<T*>(out_h), static_cast<T*>(out_rn), rows, C)
+    if (nv <= 1) DGPT_MIXV(1);
+    else if (nv <= 2) DGPT_MIXV(2);
+    else if (nv <= 3) DGPT_MIXV(3);
+    else if (nv <= 4) DGPT_MIXV(4);
+    else DGPT_MIXV(8);
+#undef DGPT_MIXV
+    return launch_status("depthmix");
+  }
   const int epl = (C + 31) / 32;
 #define DGPT_MIX(E)                                                                        \
   depthmix_kernel<T, E><<<grid, warps * 32, 0, st>>>(cp, n, static_cast<const T*>(w),      \
