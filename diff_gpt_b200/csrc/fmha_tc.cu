@@ -111,6 +111,40 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// as tmem_ld32 but without the wait: the caller issues tc_wait_ld() once after a batch of loads
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t addr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr)
+      : "memory");
+}
+
+// 32 consecutive fp32 columns of this thread's TMEM lane, written back
+__device__ __forceinline__ void tmem_st32(uint32_t addr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(addr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
+        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+
 // 16 consecutive 32-bit columns (32 packed bf16) of this thread's TMEM lane
 __device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16]) {
   asm volatile(
@@ -243,9 +277,6 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
     }
   };
 
-  float acc[D];
-#pragma unroll
-  for (int d = 0; d < D; ++d) acc[d] = 0.f;
   float m = -INFINITY, l = 0.f;
   bool fail = false;
   int pend_k = -1, pend_v = -1, pend_s = -1, pend_o = -1;  // thread 0: parity of an outstanding phase, or -1
@@ -306,57 +337,71 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
     // ---- softmax of this row ----
     const bool need_mask = (t0 + kBN > klen) || (p.causal && t0 + kBN - 1 > p.q_offset + q0);
     const int last_key = p.causal ? min(klen - 1, p.q_offset + q0 + tid) : klen - 1;
+    float sv[kBN];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) tmem_ld32_nowait(lane_addr + c * 32, &sv[c * 32]);
+    tc_wait_ld();
     float mx = -INFINITY;
+    if (need_mask) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      float v[32];
-      tmem_ld32(lane_addr + c * 32, v);
+      for (int i = 0; i < kBN; ++i) {
+        sv[i] = (t0 + i <= last_key) ? sv[i] : -INFINITY;
+        mx = fmaxf(mx, sv[i]);
+      }
+    } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const bool vis = !need_mask || (t0 + c * 32 + i <= last_key);
-        mx = fmaxf(mx, vis ? v[i] : -INFINITY);
+      for (int i = 0; i < kBN; ++i) mx = fmaxf(mx, sv[i]);
+    }
+    // Lazy rescale: the running maximum only moves when the new one exceeds it by 2^8, so the
+    // output accumulator in TMEM is touched rarely.  Exponents then stay below 2^8.
+    const float mx2 = mx * p.scale_log2;
+    float alpha = 1.f;
+    if (mx2 > m + 8.f || m == -INFINITY) {
+      alpha = (m == -INFINITY) ? 0.f : ex2(m - mx2);
+      m = mx2;
+    }
+    if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float v[32];
+        tmem_ld32(lane_addr + 128 + c * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= alpha;
+        tmem_st32(lane_addr + 128 + c * 32, v);
       }
     }
-    const float m_new = fmaxf(m, mx * p.scale_log2);
-    const float alpha = (m == -INFINITY) ? 0.f : ex2(m - m_new);
-    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+    const float m_use = (m == -INFINITY) ? 0.f : m;
     float rowsum = 0.f;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      float v[32];
-      tmem_ld32(lane_addr + c * 32, v);
       uint32_t packed[16];
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
-        const bool v0 = !need_mask || (t0 + c * 32 + i <= last_key);
-        const bool v1 = !need_mask || (t0 + c * 32 + i + 1 <= last_key);
-        const float p0 = v0 ? ex2(v[i] * p.scale_log2 - m_use) : 0.f;
-        const float p1 = v1 ? ex2(v[i + 1] * p.scale_log2 - m_use) : 0.f;
+        const float p0 = ex2(fmaf(sv[c * 32 + i], p.scale_log2, -m_use));      // -inf -> 0
+        const float p1 = ex2(fmaf(sv[c * 32 + i + 1], p.scale_log2, -m_use));
         rowsum += p0 + p1;
         const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
         packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
       }
-      tmem_st16(lane_addr + c * 16, packed);  // P overwrites the part of S this row has already consumed
+      tmem_st16(lane_addr + c * 16, packed);  // P overwrites S, which this row now holds in registers
     }
     l = l * alpha + rowsum;
-    m = m_new;
     tc_wait_st();
     tc_fence_before();
     if (__syncthreads_or(fail ? 1 : 0)) {
       fail = true;
       break;
     }
-    // ---- O_tile = P V ----
+    // ---- O += P V (accumulated in TMEM across tiles) ----
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < kBN / 16; ++ks)
-        umma_ts(tmem + 128, tmem + ks * 8, smem_desc(aV + ks * 2048, kSubBytes, 1024), kIdescPV, ks > 0 ? 1u : 0u);
+        umma_ts(tmem + 128, tmem + ks * 8, smem_desc(aV + ks * 2048, kSubBytes, 1024), kIdescPV,
+                (j > 0 || ks > 0) ? 1u : 0u);
       umma_commit(bar_o);
       pend_o = (int)par;
     }
-#pragma unroll
-    for (int d = 0; d < D; ++d) acc[d] *= alpha;
     if (!wait_or_abort(bar_o, par, abort_flag)) fail = true;
     tc_fence_after();
     if (tid == 0 && !fail) {
@@ -365,13 +410,6 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
         load_kv(&mv, aV, bar_v, j + 1);
         pend_v = (int)(par ^ 1u);
       }
-    }
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c) {
-      float v[32];
-      tmem_ld32(lane_addr + 128 + c * 32, v);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) acc[c * 32 + i] += v[i];
     }
     tc_fence_before();
     if (__syncthreads_or(fail ? 1 : 0)) {
@@ -383,23 +421,26 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
   if (!fail) {
     const int qi = q0 + tid;
     if (qi < p.Tq) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const float inv = (l > 0.f && n_tiles > 0) ? 1.f / l : 0.f;
       const long long off = (long long)b * p.o_bs + (long long)qi * p.o_rs + (long long)h * D;
-      if (p.o_f32) {
-        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.o) + off);
 #pragma unroll
-        for (int d = 0; d < D; d += 4)
-          dst[d >> 2] = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
-      } else {
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.o) + off);
+      for (int c = 0; c < D / 32; ++c) {
+        float v[32];
+        if (n_tiles > 0) {
+          tmem_ld32(lane_addr + 128 + c * 32, v);
+        } else {
 #pragma unroll
-        for (int d = 0; d < D; d += 8) {
-          __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[d] * inv, acc[d + 1] * inv);
-          __nv_bfloat162 h1 = __floats2bfloat162_rn(acc[d + 2] * inv, acc[d + 3] * inv);
-          __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[d + 4] * inv, acc[d + 5] * inv);
-          __nv_bfloat162 h3 = __floats2bfloat162_rn(acc[d + 6] * inv, acc[d + 7] * inv);
-          dst[d >> 3] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
-                                   *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+          for (int i = 0; i < 32; ++i) v[i] = 0.f;
+        }
+        if (p.o_f32) {
+          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.o) + off + c * 32);
+#pragma unroll
+          for (int d = 0; d < 32; d += 4)
+            dst[d >> 2] = make_float4(v[d] * inv, v[d + 1] * inv, v[d + 2] * inv, v[d + 3] * inv);
+        } else {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.o) + off + c * 32;
+#pragma unroll
+          for (int d = 0; d < 32; d += 8) st16<__nv_bfloat16>(dst + d, v + d, inv);
         }
       }
       if (p.lse) p.lse[((long long)b * p.Tq + qi) * p.H + h] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;

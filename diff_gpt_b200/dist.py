@@ -40,9 +40,9 @@ def gather_trajectories(local: torch.Tensor, n_total: int, group=None) -> torch.
     if n_local < width:
         pad = torch.zeros((S, width - n_local, G), dtype=local.dtype, device=local.device)
         block = torch.cat([local, pad], dim=1)
-    out = torch.empty((world, S, width, G), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(out, block.contiguous(), group=group)
-    parts = [out[r, :, : shard_range(n_total, r, world)[1]] for r in range(world)]
+    out = [torch.empty((S, width, G), dtype=local.dtype, device=local.device) for _ in range(world)]
+    dist.all_gather(out, block.contiguous(), group=group)
+    parts = [out[r][:, : shard_range(n_total, r, world)[1]] for r in range(world)]
     return torch.cat(parts, dim=1)
 
 
