@@ -21,7 +21,7 @@ namespace tc {
 constexpr int kBM = 128;          // queries per CTA
 constexpr int kBN = 128;          // keys per tile
 constexpr int kTmemCols = 256;    // S/P: [0,128), O tile: [128, 128 + D)
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait here
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -42,11 +42,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false if the phase did not complete within kSpinLimit polls.
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false if the phase did not complete within kWaitLimitNs.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_ns() - t0 > kWaitLimitNs) return false;
+  }
 }
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2,
@@ -196,9 +204,12 @@ struct Params {
 
 // Bounded wait that also gives up early when another thread has raised the CTA's abort flag.
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  const unsigned long long t0 = global_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > kWaitLimitNs) break;
   }
   *abort_flag = 1;
   return false;
@@ -419,19 +430,21 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
   }
 
   if (!fail) {
+    // tcgen05.ld is warp-collective: every thread reads its row, only rows that exist are stored
     const int qi = q0 + tid;
-    if (qi < p.Tq) {
-      const float inv = (l > 0.f && n_tiles > 0) ? 1.f / l : 0.f;
-      const long long off = (long long)b * p.o_bs + (long long)qi * p.o_rs + (long long)h * D;
+    const bool row_ok = qi < p.Tq;
+    const float inv = (l > 0.f && n_tiles > 0) ? 1.f / l : 0.f;
+    const long long off = (long long)b * p.o_bs + (long long)qi * p.o_rs + (long long)h * D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        float v[32];
-        if (n_tiles > 0) {
-          tmem_ld32(lane_addr + 128 + c * 32, v);
-        } else {
+    for (int c = 0; c < D / 32; ++c) {
+      float v[32];
+      if (n_tiles > 0) {  // CTA-uniform
+        tmem_ld32(lane_addr + 128 + c * 32, v);
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0.f;
-        }
+        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+      }
+      if (row_ok) {
         if (p.o_f32) {
           float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.o) + off + c * 32);
 #pragma unroll
@@ -443,8 +456,8 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
           for (int d = 0; d < 32; d += 8) st16<__nv_bfloat16>(dst + d, v + d, inv);
         }
       }
-      if (p.lse) p.lse[((long long)b * p.Tq + qi) * p.H + h] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
     }
+    if (row_ok && p.lse) p.lse[((long long)b * p.Tq + qi) * p.H + h] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
   } else if (tid == 0) {
     // a wait ran out: record it, then give whatever is still in flight a bounded chance to land
     if (p.status) atomicExch(p.status, 2);
