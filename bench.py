@@ -227,7 +227,7 @@ def run_ours(args) -> None:
     def series_of(step_idx: int) -> list[int]:
         return [(step_idx * series_per_step + j) % N_SERIES for j in range(series_per_step)]
 
-    def device_step(step_idx: int, use_graph: bool = True):
+    def device_step(step_idx: int, use_graph: bool = not args.no_graph):
         ids = series_of(step_idx)
         run = DecodeRun(
             model, prompts_dev[torch.tensor(ids, device=dev)], n_local, HORIZON, sampler, 42, None,
@@ -267,7 +267,7 @@ def run_ours(args) -> None:
     assert out.shape == (series_per_step, TRAJECTORIES, HORIZON) and int(out.min()) >= 0 and int(out.max()) < CFG4["vocab_size"]
 
     # ---- end to end: host prompts in, host tokens out, through the public engine call ----
-    e2e_steps = max(1, min(args.steps, 2))
+    e2e_steps = 0 if args.no_e2e else max(1, min(args.steps, 2))
     pinned = torch.empty((series_per_step, TRAJECTORIES, HORIZON), dtype=torch.int32).pin_memory()
     barrier()
     t0 = time.perf_counter()
@@ -285,7 +285,7 @@ def run_ours(args) -> None:
         t = torch.tensor([e2e_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
-    e2e = {
+    e2e = None if e2e_steps == 0 else {
         "value": e2e_steps * tokens_per_step / e2e_s, "unit": "tokens/s",
         "h2d_bytes_per_step": series_per_step * PROMPT_TOKENS * 4,
         "d2h_bytes_per_step": series_per_step * TRAJECTORIES * HORIZON * 4,
@@ -373,7 +373,13 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-kernel-pass", action="store_true", help="skip the per-kernel timing step")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg")
+    ap.add_argument("--no-graph", action="store_true", help="launch the decode steps eagerly (for profilers)")
+    ap.add_argument("--small", action="store_true",
+                    help="profiling case: 2048 trajectories x 64 steps (4.8 GB of KV), same model and prompt")
     args = ap.parse_args()
+    if args.small:
+        globals().update(TRAJECTORIES=2048, HORIZON=64)
     if args.impl == "reference":
         run_reference(args)
     else:
