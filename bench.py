@@ -365,8 +365,75 @@ def roofline(kernels: dict, rows: int, n_series: int) -> dict:
             "traffic": None, "launches": k["launches"], "avg_launch_ms": k["avg_ms"]}
 
 
+def kernel_case(name: str, iters: int = 5) -> None:
+    """One kernel alone on a case sized for an `ncu --set full` capture (a few launches, < 2 GB touched).
+
+    decode_attn: config-4 shapes at decode step 128 — 4096 trajectories x 12 heads, head_dim 64, 128 own
+                 tokens per trajectory in 64-token pages, prompt partial merged, gate applied.
+    fmha:        config-5 shapes at S = 4096 — batch 8, 16 heads, head_dim 128, causal, dense K/V.
+    Prints one JSON line with the CUDA-event time per launch and the achieved rate.
+    """
+    from diff_gpt_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    pk = peaks()
+    if name == "decode_attn":
+        R, H, D, pt, own = TRAJECTORIES, CFG4["n_head"], 64, 64, 128
+        C = H * D
+        pages = own // pt
+        pool = torch.randn((R * pages, 2, H, pt, D), device=dev, dtype=torch.bfloat16, generator=g)
+        table = torch.arange(R * pages, dtype=torch.int32, device=dev).view(R, pages)
+        lay = ops.kv_layout(pool[0, 0], pool[0, 1], 2 * H * pt * D, pt * D, pt, table, n_pages=R * pages)
+        q = torch.randn((R, C), device=dev, dtype=torch.bfloat16, generator=g)
+        gate = torch.randn((R, C), device=dev, dtype=torch.bfloat16, generator=g)
+        y = torch.empty_like(q)
+        po = torch.randn((R, H, D), device=dev, dtype=torch.float32, generator=g)
+        pl = torch.randn((R, H), device=dev, dtype=torch.float32, generator=g)
+        zero = torch.zeros(R, dtype=torch.int32, device=dev)
+        n1 = torch.full((R,), own, dtype=torch.int32, device=dev)
+
+        def launch():
+            ops.decode_attn(q, lay, zero, zero, n1, None, y, H=H, D=D, gate=gate, prefix_o=po, prefix_lse=pl)
+
+        work = R * (2 * C * 2 * own + 3 * C * 2 + C * 4 + H * 4)
+        unit, peak = "GB/s", pk["hbm_gbs"]
+    elif name == "fmha":
+        B, H, S, D = 8, 16, 4096, 128
+        q = torch.randn((B, S, H, D), device=dev, dtype=torch.bfloat16, generator=g)
+        kv = torch.randn((B, 2, H, S, D), device=dev, dtype=torch.bfloat16, generator=g)
+        lay = ops.kv_layout(kv[0, 0], kv[0, 1], 2 * H * S * D, S * D, S)
+        o = torch.empty_like(q)
+        st = torch.zeros(1, dtype=torch.int32, device=dev)
+
+        def launch():
+            ops.fmha_prefill(q, lay, o, B=B, H=H, Tq=S, D=D, q_batch_stride=S * H * D, q_row_stride=H * D,
+                             o_batch_stride=S * H * D, o_row_stride=H * D, kv_len_all=S, causal=True, impl=2, status=st)
+
+        work = 2 * B * H * S * S * D
+        unit, peak = "TFLOP/s", pk["bf16_tflops"]
+    else:
+        raise SystemExit(f"unknown kernel case {name}")
+    for _ in range(3):
+        launch()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        launch()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / iters
+    rate = work / (ms / 1e3) / (1e9 if unit == "GB/s" else 1e12)
+    print(json.dumps({"kernel_case": name, "ms_per_launch": ms, "achieved": rate, "unit": unit, "peak": peak,
+                      "frac": rate / peak, "algorithmic_work_per_launch": work, "peak_source": pk["source"]}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel-case", default=None, choices=["decode_attn", "fmha"],
+                    help="run one kernel alone on a small case (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
@@ -380,6 +447,9 @@ def main() -> None:
     args = ap.parse_args()
     if args.small:
         globals().update(TRAJECTORIES=2048, HORIZON=64)
+    if args.kernel_case:
+        kernel_case(args.kernel_case)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -35,8 +35,15 @@ __device__ __forceinline__ void merge_partial(float& m, float& l, float* acc, fl
   m = mn;
 }
 
+#ifndef DGPT_DEC_U
+#define DGPT_DEC_U 8        // 16-byte loads in flight per lane and per tensor
+#endif
+#ifndef DGPT_DEC_MINB
+#define DGPT_DEC_MINB 4     // minimum resident CTAs per SM asked of the compiler
+#endif
+
 template <typename T, int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, DGPT_DEC_MINB)
 decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const int* __restrict__ len0,
                    const int* __restrict__ start1, const int* __restrict__ len1, const int* __restrict__ step_ptr,
                    const float* __restrict__ prefix_o, const float* __restrict__ prefix_lse,
@@ -72,7 +79,7 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
 
   const T* kbase = static_cast<const T*>(kv.k);
   const T* vbase = static_cast<const T*>(kv.v);
-  constexpr int U = 4;  // 16-byte loads in flight per lane and per tensor
+  constexpr int U = DGPT_DEC_U;
   // Walk the keys page by page: one page-table lookup per page, then a dense run of tokens.
   for (int i = begin; i < end;) {  // every quantity below is warp-uniform
     const bool in0 = i < n0;
@@ -89,6 +96,7 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
       for (int u = 0; u < U; ++u) {
         const int t = t0 + u * TPW + g;
         ok[u] = t < cnt;
+        kr[u] = vr[u] = make_uint4(0u, 0u, 0u, 0u);
         if (ok[u]) {
           kr[u] = *reinterpret_cast<const uint4*>(kbase + base + (long long)t * D);
           vr[u] = *reinterpret_cast<const uint4*>(vbase + base + (long long)t * D);
@@ -102,7 +110,7 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
         float d = 0.f;
 #pragma unroll
         for (int x = 0; x < VEC; ++x) d += qf[x] * kf[x];
-        s[u] = ok[u] ? d : 0.f;
+        s[u] = d;  // 0 for a token past the end (its registers were cleared)
       }
 #pragma unroll
       for (int o = LPT >> 1; o > 0; o >>= 1) {
@@ -125,7 +133,7 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
           unpack16<T>(vr[u], vf);
           l += pw;
 #pragma unroll
-          for (int x = 0; x < VEC; ++x) acc[x] += pw * (ok[u] ? vf[x] : 0.f);
+          for (int x = 0; x < VEC; ++x) acc[x] += pw * vf[x];
         }
         m = mn;
       }
