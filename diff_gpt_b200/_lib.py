@@ -60,6 +60,11 @@ PROTOTYPES = {
         C.c_int,
         [_p, _i64, _kvp, _p, _p, _p, _p, _p, _p, _p, _i64, _p, _i64, _p, _sz, _i32, _i32, _i32, _i32, _i32, _p],
     ),
+    "dgpt_decode_attn_static_capacity_bytes": (_sz, []),
+    "dgpt_decode_attn_static": (
+        C.c_int,
+        [_p, _i64, _kvp, _p, _p, _p, _p, _p, _p, _p, _i64, _p, _i64, _i32, _i32, _i32, _i32, _i32, _p],
+    ),
     "dgpt_swiglu": (C.c_int, [_p, _p, _i64, _i32, _f32, _f32, _i32, _p]),
     "dgpt_sigmoid_gate": (C.c_int, [_p, _i64, _p, _i64, _i64, _i32, _i32, _p]),
     "dgpt_softcap": (C.c_int, [_p, _i64, _f32, _i32, _p]),
@@ -70,7 +75,9 @@ PROTOTYPES = {
     ),
     "dgpt_nucleus_filter": (C.c_int, [_p, _i64, _p, _i64, _i32, _i32, _f32, _i32, _p]),
 }
-_NOT_LAUNCHING = {"dgpt_last_error", "dgpt_version", "dgpt_decode_attn_workspace_bytes"}
+_NOT_LAUNCHING = {
+    "dgpt_last_error", "dgpt_version", "dgpt_decode_attn_workspace_bytes", "dgpt_decode_attn_static_capacity_bytes",
+}
 
 
 class Stats:

@@ -301,3 +301,91 @@ extern "C" int dgpt_decode_attn(const void* q, int64_t q_row_stride, const dgpt_
   set_error("decode_attn: dtype %d with head_dim %d is not built", dtype, D);
   return DGPT_E_UNSUPPORTED;
 }
+
+// ---- split-K decode attention for callers that cannot allocate ------------------------------------
+// The split-K partials normally live in a workspace the caller allocates.  Some callers have no
+// allocator at hand at the point where they launch: code running under a framework that forbids
+// cudaMalloc on its hot path, a plugin that is handed only its input and output buffers, or a
+// latency-critical loop that must not touch the allocator.  For them the partials go into this
+// fixed array, which every GPU that loads the library carries until the process exits.
+namespace dgpt {
+constexpr size_t kStaticScratchFloats = (size_t)4 << 20;  // 16 MiB
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_scratch_addr[kMaxDevices];  // device address of the array, per device, filled on first use
+
+// Host code sees `g_decode_scratch` only as a stand-in for the symbol; the address a kernel can use has
+// to be asked for, with the device that will run the kernel current.
+static int scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_error("decode_attn_static: cannot identify the current device (%s)", cudaGetErrorString(e));
+    return DGPT_E_CUDA;
+  }
+  if (g_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("decode_attn_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      return DGPT_E_CUDA;
+    }
+    g_scratch_addr[dev] = static_cast<float*>(p);
+  }
+  *out = g_scratch_addr[dev];
+  return DGPT_OK;
+}
+}  // namespace dgpt
+
+extern "C" size_t dgpt_decode_attn_static_capacity_bytes(void) { return dgpt::kStaticScratchFloats * sizeof(float); }
+
+extern "C" int dgpt_decode_attn_static(const void* q, int64_t q_row_stride, const dgpt_kv_layout* kv,
+                                       const int32_t* len0, const int32_t* start1, const int32_t* len1,
+                                       const int32_t* step_ptr, const float* prefix_o, const float* prefix_lse,
+                                       const void* gate, int64_t gate_row_stride, void* y, int64_t y_row_stride,
+                                       int32_t n_splits, int32_t R, int32_t H, int32_t D, int32_t dtype,
+                                       void* stream) {
+  DGPT_REQUIRE(q && y && len0 && start1 && len1, "decode_attn_static: NULL pointer");
+  DGPT_REQUIRE(R >= 0 && H > 0 && n_splits >= 1 && n_splits <= 65535, "decode_attn_static: bad sizes");
+  DGPT_REQUIRE((prefix_o == nullptr) == (prefix_lse == nullptr), "decode_attn_static: prefix_o and prefix_lse go together");
+  DGPT_REQUIRE(q_row_stride % 8 == 0 && y_row_stride % 8 == 0 && gate_row_stride % 8 == 0,
+               "decode_attn_static: row strides must be multiples of 8 elements");
+  if (int e = validate_kv(kv, D)) return e;
+  if (R == 0) return DGPT_OK;
+  const size_t need = dgpt_decode_attn_workspace_bytes(R, H, D, n_splits);
+  if (need > dgpt_decode_attn_static_capacity_bytes()) {
+    set_error("decode_attn_static: R=%d H=%d D=%d n_splits=%d needs %zu bytes of partials, the built-in scratch holds %zu; "
+              "use fewer splits or dgpt_decode_attn with a caller workspace",
+              R, H, D, n_splits, need, dgpt_decode_attn_static_capacity_bytes());
+    return DGPT_E_WORKSPACE;
+  }
+  float* ws = nullptr;
+  if (int e = scratch_for_current_device(&ws)) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const KvView view = make_view(kv);
+#define DGPT_DECS(TT, DD)                                                                                        \
+  return decode_launch<TT, DD>(q, q_row_stride, view, len0, start1, len1, step_ptr, prefix_o, prefix_lse, gate, \
+                               gate_row_stride, y, y_row_stride, ws, n_splits, R, H, st)
+  if (dtype == DGPT_F32) {
+    switch (D) {
+      case 8: DGPT_DECS(float, 8);
+      case 16: DGPT_DECS(float, 16);
+      case 32: DGPT_DECS(float, 32);
+      case 64: DGPT_DECS(float, 64);
+      case 128: DGPT_DECS(float, 128);
+    }
+  } else if (dtype == DGPT_BF16) {
+    switch (D) {
+      case 8: DGPT_DECS(__nv_bfloat16, 8);
+      case 16: DGPT_DECS(__nv_bfloat16, 16);
+      case 32: DGPT_DECS(__nv_bfloat16, 32);
+      case 64: DGPT_DECS(__nv_bfloat16, 64);
+      case 128: DGPT_DECS(__nv_bfloat16, 128);
+      case 256: DGPT_DECS(__nv_bfloat16, 256);
+    }
+  }
+#undef DGPT_DECS
+  set_error("decode_attn_static: dtype %d with head_dim %d is not built", dtype, D);
+  return DGPT_E_UNSUPPORTED;
+}

@@ -181,6 +181,43 @@ def decode_attn(
     )
 
 
+def decode_attn_static_capacity_bytes() -> int:
+    return int(lib.dgpt_decode_attn_static_capacity_bytes())
+
+
+def decode_attn_static(
+    q: torch.Tensor,
+    kv: KvLayout,
+    len0: torch.Tensor,
+    start1: torch.Tensor,
+    len1: torch.Tensor,
+    step: torch.Tensor | None,
+    y: torch.Tensor,
+    *,
+    H: int,
+    D: int,
+    gate: torch.Tensor | None = None,
+    prefix_o: torch.Tensor | None = None,
+    prefix_lse: torch.Tensor | None = None,
+    n_splits: int = 1,
+) -> None:
+    """`decode_attn` with the split-K partials kept in the library's built-in 16 MiB array.
+
+    For hosts that may not allocate device memory where they launch (memory handed out once at start-up,
+    plugins that own only their inputs and outputs).  Raises `DgptError` when the partials would not fit.
+    Calls share the array: do not let two of them overlap on the GPU.  Make the first call on a device
+    outside stream capture.
+    """
+    _cuda(q, len0, start1, len1, step, y, gate, prefix_o, prefix_lse)
+    check(
+        lib.dgpt_decode_attn_static(
+            q.data_ptr(), q.stride(0), C.byref(kv), len0.data_ptr(), start1.data_ptr(), len1.data_ptr(), _ptr(step),
+            _ptr(prefix_o), _ptr(prefix_lse), _ptr(gate), 0 if gate is None else gate.stride(0), y.data_ptr(),
+            y.stride(0), n_splits, q.shape[0], H, D, dtype_code(q), _stream(),
+        )
+    )
+
+
 def swiglu(x: torch.Tensor, out: torch.Tensor, alpha: float, limit: float) -> None:
     _cuda(x, out)
     assert x.is_contiguous() and out.is_contiguous() and x.shape[-1] == 2 * out.shape[-1]

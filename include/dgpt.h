@@ -134,6 +134,32 @@ int dgpt_decode_attn(const void* q, int64_t q_row_stride, const dgpt_kv_layout* 
                      size_t workspace_bytes, int32_t n_splits, int32_t R, int32_t H, int32_t D,
                      int32_t dtype, void* stream);
 
+/* dgpt_decode_attn for callers that cannot allocate device memory.  (No counterpart in the reference:
+ * its attention never needs scratch memory.)
+ * Who needs it: a host that must not call cudaMalloc where it launches — an inference server whose
+ * memory is handed out once at start-up, a plugin that receives nothing but its input and output
+ * buffers, a real-time loop that may not enter the allocator.  With n_splits > 1 the kernel has to
+ * park per-split partial results somewhere; here they go into a fixed 16 MiB array that is part of the
+ * library image (every GPU that loads the library keeps that array until the process exits), so the
+ * caller passes only inputs and outputs, and the call performs no cudaMalloc/cudaFree and uses no
+ * allocating library routine.
+ * Limits and rules:
+ *   - R * H * n_splits * (D + 2) * 4 bytes must fit in dgpt_decode_attn_static_capacity_bytes()
+ *     (16 MiB); larger requests return DGPT_E_WORKSPACE with the numbers in dgpt_last_error.
+ *   - The first call on each device looks up the array's device address (with that device current);
+ *     make that first call before starting any stream capture.
+ *   - All calls share the one array and it keeps the previous call's contents.  Nothing in it has to
+ *     start at zero: every (split, row, head) slot is rewritten by the first pass before the combine
+ *     pass reads it.  Two calls that overlap on the GPU (different streams, or graphs replayed
+ *     concurrently) race on it: serialise them.
+ * Arguments are those of dgpt_decode_attn without the workspace pair; results are identical. */
+size_t dgpt_decode_attn_static_capacity_bytes(void);
+int dgpt_decode_attn_static(const void* q, int64_t q_row_stride, const dgpt_kv_layout* kv,
+                            const int32_t* len0, const int32_t* start1, const int32_t* len1,
+                            const int32_t* step_ptr, const float* prefix_o, const float* prefix_lse,
+                            const void* gate, int64_t gate_row_stride, void* y, int64_t y_row_stride,
+                            int32_t n_splits, int32_t R, int32_t H, int32_t D, int32_t dtype, void* stream);
+
 /* out[r, j] = g*sigmoid(alpha*g)*(l+1) with g = min(in[r,2j], limit), l = clamp(in[r,2j+1], -limit, limit).
  * Replaces src/diff_gpt/model/swi_glu.py:11-19.  in: [rows, 2*n_out]; out: [rows, n_out]. */
 int dgpt_swiglu(const void* in, void* out, int64_t rows, int32_t n_out, float alpha, float limit,
