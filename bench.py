@@ -227,7 +227,7 @@ def run_ours(args) -> None:
     def series_of(step_idx: int) -> list[int]:
         return [(step_idx * series_per_step + j) % N_SERIES for j in range(series_per_step)]
 
-    def device_step(step_idx: int, use_graph: bool = not args.no_graph):
+    def device_step(step_idx: int, use_graph: bool = not args.no_graph, gather: bool = True):
         ids = series_of(step_idx)
         run = DecodeRun(
             model, prompts_dev[torch.tensor(ids, device=dev)], n_local, HORIZON, sampler, 42, None,
@@ -236,7 +236,7 @@ def run_ours(args) -> None:
         run.start()
         run.advance(HORIZON)
         toks = run.history.view(series_per_step, n_local, HORIZON)
-        return gather_trajectories(toks, TRAJECTORIES), run
+        return (gather_trajectories(toks, TRAJECTORIES) if gather else toks), run
 
     def barrier():
         if world > 1:
@@ -297,7 +297,7 @@ def run_ours(args) -> None:
     if rank == 0 and not args.no_kernel_pass:
         timer = _lib.KernelTimer()
         with _lib.timed(timer):
-            _, run = device_step(args.warmup + args.steps, use_graph=False)
+            _, run = device_step(args.warmup + args.steps, use_graph=False, gather=False)  # rank 0 alone: no collective
         torch.cuda.synchronize(dev)
         del run
         kernels = {k: {kk: round(vv, 4) if isinstance(vv, float) else vv for kk, vv in v.items()} for k, v in timer.summary().items()}
