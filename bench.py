@@ -413,6 +413,16 @@ def kernel_case(name: str, iters: int = 5) -> None:
 
         work = 2 * B * H * S * S * D
         unit, peak = "TFLOP/s", pk["bf16_tflops"]
+    elif name == "sample":
+        R, V = TRAJECTORIES, CFG4["vocab_size"]
+        logits = (torch.randn((R, V), device=dev, generator=g) * 0.05).to(torch.bfloat16)  # near-flat, as at random init
+        out = torch.empty(R, dtype=torch.int32, device=dev)
+
+        def launch():
+            ops.sample(logits, out, cap=15.0, temperature=TEMPERATURE, top_p=TOP_P, seed=42)
+
+        work = R * V * 2
+        unit, peak = "GB/s", pk["hbm_gbs"]
     else:
         raise SystemExit(f"unknown kernel case {name}")
     for _ in range(3):
@@ -432,7 +442,7 @@ def kernel_case(name: str, iters: int = 5) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel-case", default=None, choices=["decode_attn", "fmha"],
+    ap.add_argument("--kernel-case", default=None, choices=["decode_attn", "fmha", "sample"],
                     help="run one kernel alone on a small case (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)

@@ -96,6 +96,78 @@ __global__ void rope_qknorm_kvappend_kernel(const T* __restrict__ q, const T* __
   }
 }
 
+// Vector variant: LPH = D / VEC lanes own one (token, head), each lane one 16-byte vector (VEC / 2
+// rotation pairs) of q, k, v and of the (cos, sin) row, so a warp covers 32 / LPH heads and every
+// access is 16 bytes wide.  Same rounding points as the scalar kernel.
+template <typename T, int D>
+__global__ void rope_qknorm_kvappend_vec_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                                const T* __restrict__ v, long long in_stride, T* __restrict__ q_out,
+                                                long long q_out_stride, const T* __restrict__ cs, int table_len,
+                                                KvView kv, const int* __restrict__ seq_pos0,
+                                                const int* __restrict__ seq_slot0, const int* __restrict__ step_ptr,
+                                                int n_seq, int T_len, int H, int* __restrict__ status) {
+  constexpr int VEC = Io<T>::kVec16;
+  constexpr int LPH = D / VEC;
+  static_assert(LPH >= 1 && LPH <= 32 && (LPH & (LPH - 1)) == 0, "unsupported head_dim");
+  const long long unit = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LPH;  // (token, head)
+  const int e = threadIdx.x % LPH;
+  const long long total = (long long)n_seq * T_len * H;
+  const bool live = unit < total;
+  const long long u = live ? unit : total - 1;  // idle lanes shadow the last unit so that shuffles stay full
+  const int h = (int)(u % H);
+  const long long tok = u / H;
+  const int s = (int)(tok / T_len), t = (int)(tok - (long long)s * T_len);
+  const int step = step_ptr ? *step_ptr : 0;
+  const int pos = seq_pos0[s] + step + t;
+  const int slot = seq_slot0[s] + step + t;
+  const int cap = kv.page_table ? kv.max_pages * kv.page_tokens : kv.page_tokens;
+  const bool in_range = pos >= 0 && pos < table_len && slot >= 0 && slot < cap;
+  if (live && !in_range && e == 0) atomicExch(status, 1);
+  const int pos_c = in_range ? pos : 0;
+  const long long src = tok * in_stride + (long long)h * D + e * VEC;
+  float qf[VEC], kf[VEC], cf[VEC];
+  ld16<T>(q + src, qf);
+  ld16<T>(k + src, kf);
+  ld16<T>(cs + (long long)pos_c * D + e * VEC, cf);  // (cos, sin) pairs of this lane's rotation pairs
+  const uint4 vraw = *reinterpret_cast<const uint4*>(v + src);
+  float qss = 0.f, kss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; i += 2) {
+    const float c = cf[i], sn = cf[i + 1];
+    const float qa = Io<T>::round(qf[i] * c - qf[i + 1] * sn), qb = Io<T>::round(qf[i] * sn + qf[i + 1] * c);
+    const float ka = Io<T>::round(kf[i] * c - kf[i + 1] * sn), kb = Io<T>::round(kf[i] * sn + kf[i + 1] * c);
+    qf[i] = qa; qf[i + 1] = qb; kf[i] = ka; kf[i + 1] = kb;
+    qss += qa * qa + qb * qb;
+    kss += ka * ka + kb * kb;
+  }
+#pragma unroll
+  for (int o = LPH >> 1; o > 0; o >>= 1) {
+    qss += __shfl_xor_sync(0xffffffffu, qss, o);
+    kss += __shfl_xor_sync(0xffffffffu, kss, o);
+  }
+  if (!live || !in_range) return;
+  const float qinv = rsqrtf(qss / (float)D + kRmsEps);
+  const float kinv = rsqrtf(kss / (float)D + kRmsEps);
+  const long long off = kv_offset(kv, s, h, slot, D) + e * VEC;
+  st16<T>(q_out + tok * q_out_stride + (long long)h * D + e * VEC, qf, qinv);
+  st16<T>(static_cast<T*>(kv.k) + off, kf, kinv);
+  *reinterpret_cast<uint4*>(static_cast<T*>(kv.v) + off) = vraw;
+}
+
+template <typename T, int D>
+static int rope_vec_launch(const void* q, const void* k, const void* v, long long in_stride, void* q_out,
+                           long long q_out_stride, const void* cs, int table_len, const KvView& view,
+                           const int* pos0, const int* slot0, const int* step_ptr, int n_seq, int T_len, int H,
+                           int* status, cudaStream_t st) {
+  constexpr int LPH = D / Io<T>::kVec16;
+  const long long threads = (long long)n_seq * T_len * H * LPH;
+  const unsigned grid = (unsigned)((threads + 255) / 256);
+  rope_qknorm_kvappend_vec_kernel<T, D><<<grid, 256, 0, st>>>(
+      static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), in_stride, static_cast<T*>(q_out),
+      q_out_stride, static_cast<const T*>(cs), table_len, view, pos0, slot0, step_ptr, n_seq, T_len, H, status);
+  return launch_status("rope_qknorm_kvappend");
+}
+
 }  // namespace dgpt
 
 using namespace dgpt;
@@ -117,6 +189,33 @@ extern "C" int dgpt_rope_qknorm_kvappend(const void* q, const void* k, const voi
   const unsigned grid = (unsigned)((total + warps - 1) / warps);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const KvView view = make_view(kv);
+  {
+    auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const int vec = dtype == DGPT_BF16 ? 8 : 4;
+    const bool aligned = al(q) && al(k) && al(v) && al(q_out) && al(cs_table) && in_row_stride % vec == 0 &&
+                         q_out_row_stride % vec == 0 && D % vec == 0;
+#define DGPT_ROPE(TT, DD)                                                                                         \
+  return rope_vec_launch<TT, DD>(q, k, v, in_row_stride, q_out, q_out_row_stride, cs_table, table_len, view,      \
+                                 seq_pos0, seq_slot0, step_ptr, n_seq, T, H, status, st)
+    if (aligned && dtype == DGPT_BF16) {
+      switch (D) {
+        case 8: DGPT_ROPE(__nv_bfloat16, 8);
+        case 16: DGPT_ROPE(__nv_bfloat16, 16);
+        case 32: DGPT_ROPE(__nv_bfloat16, 32);
+        case 64: DGPT_ROPE(__nv_bfloat16, 64);
+        case 128: DGPT_ROPE(__nv_bfloat16, 128);
+      }
+    } else if (aligned && dtype == DGPT_F32) {
+      switch (D) {
+        case 8: DGPT_ROPE(float, 8);
+        case 16: DGPT_ROPE(float, 16);
+        case 32: DGPT_ROPE(float, 32);
+        case 64: DGPT_ROPE(float, 64);
+        case 128: DGPT_ROPE(float, 128);
+      }
+    }
+#undef DGPT_ROPE
+  }
   if (dtype == DGPT_F32) {
     rope_qknorm_kvappend_kernel<float><<<grid, warps * 32, 0, st>>>(
         static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v), in_row_stride,

@@ -258,12 +258,291 @@ sample_kernel(const T* __restrict__ logits, long long stride, int V, float cap, 
   }
 }
 
+// ---- one warp per row -----------------------------------------------------------------------------
+// Same rule and same draw as sample_kernel, but a row is handled by one warp with shuffles only (no
+// block barriers), four rows per CTA.  exp(z - max) of the row lives in shared memory; token i sits at
+// word i + (i >> log2(chunk)) so that both the strided sweeps and the per-lane contiguous chunks
+// (needed where token order matters) are free of bank conflicts.  The bisection stops as soon as all
+// keys left in the bracket are equal, which takes about log2(distinct keys) sweeps instead of 30.
+constexpr int kWarpRows = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(32 * kWarpRows)
+sample_warp_kernel(const T* __restrict__ logits, long long stride, int R, int V, int log2c, float cap,
+                   float temperature, float top_p, uint32_t seed_lo, uint32_t seed_hi, long long traj_id0,
+                   const long long* __restrict__ traj_ids, int step_base, const int* __restrict__ step_ptr,
+                   const int* __restrict__ force, int force_rows, long long force_stride, int* __restrict__ out_tok,
+                   int* __restrict__ out_mask, int* __restrict__ hist_tok, int* __restrict__ hist_mask,
+                   long long hist_stride) {
+  extern __shared__ __align__(16) float smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = blockIdx.x * kWarpRows + warp;
+  if (r >= R) return;
+  const int step = step_ptr ? *step_ptr : 0;
+  const int forced = force ? force[(long long)(r / force_rows) * force_stride + step] : -1;
+  int token, mask = 1;
+  if (forced >= 0) {
+    token = forced;
+    mask = 0;
+  } else {
+    float* e = smem + (size_t)warp * (V + 33);
+    auto at = [&](int i) -> float& { return e[i + (i >> log2c)]; };
+    const T* row = logits + (long long)r * stride;
+    ArgMax best{-INFINITY, 0x7fffffff};
+    for (int i = lane; i < V; i += 32) {
+      float x = Io<T>::ld(row + i);
+      if (cap > 0.f) x = Io<T>::round(cap * Io<T>::round(tanhf(Io<T>::round(x / cap))));
+      at(i) = x;
+      if (x > best.v) best = ArgMax{x, i};
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ArgMax t;
+      t.v = __shfl_xor_sync(0xffffffffu, best.v, o);
+      t.i = __shfl_xor_sync(0xffffffffu, best.i, o);
+      best = better(best, t);
+    }
+    token = best.i;
+    if (temperature != 0.f) {
+      const float zmax = best.v;
+      float part = 0.f;
+      for (int i = lane; i < V; i += 32) {
+        const float ev = __expf(at(i) - zmax);
+        at(i) = ev;
+        part += ev;
+      }
+      const float Z = warp_sum(part);
+      const bool filt = top_p < 1.f;
+      uint32_t key_b = 0u;
+      int i_cut = V;
+      const int chunk = 1 << log2c;
+      const int c0 = lane * chunk, c1 = min(V, c0 + chunk);  // this lane's tokens where order matters
+      const long long traj = traj_ids ? traj_ids[r] : traj_id0 + r;
+      // Fast path (rejection sampling): draw from softmax(z / T) over ALL tokens and accept the token if
+      // it lies in the nucleus, i.e. if the mass ranked before it is below top_p.  Accepted draws follow
+      // exactly the restricted distribution, and a draw costs two sweeps instead of a full boundary
+      // search.  Attempt a uses Philox counter word 3 = a.  If kAttempts draws are rejected (a high
+      // temperature over a tiny nucleus), the exact boundary is computed below.
+      constexpr int kAttempts = 8;
+      bool done = false;
+      {
+        __syncwarp();  // chunks below were written by other lanes
+        const float inv_t = 1.f / temperature;
+        const bool t1 = temperature == 1.f;
+        float mine = 0.f;
+        for (int i = c0; i < c1; ++i) {
+          const float ev = at(i);
+          mine += t1 ? ev : __expf(__logf(ev) * inv_t);
+        }
+        float incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float t = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += t;
+        }
+        const float W = __shfl_sync(0xffffffffu, incl, 31);
+        const float excl = incl - mine;
+        const float target = fmaxf(top_p, 1e-30f) * Z;
+        for (int a = 0; a < kAttempts && !done; ++a) {
+          const uint32_t bits = philox4x32_10((uint32_t)traj, (uint32_t)((unsigned long long)traj >> 32),
+                                              (uint32_t)(step + step_base), (uint32_t)a, seed_lo, seed_hi);
+          const float tgt = (float)(bits >> 8) * (1.0f / 16777216.0f) * W;
+          const bool own = mine > 0.f && excl <= tgt && tgt < incl;
+          int pick = best.i;
+          if (own) {
+            const float local = tgt - excl;
+            float c = 0.f;
+            for (int i = c0; i < c1; ++i) {
+              const float ev = at(i);
+              const float w = t1 ? ev : __expf(__logf(ev) * inv_t);
+              c += w;
+              if (w > 0.f) pick = i;
+              if (w > 0.f && c > local) break;
+            }
+          }
+          const unsigned who = __ballot_sync(0xffffffffu, own);
+          pick = __shfl_sync(0xffffffffu, pick, who ? __ffs(who) - 1 : 0);
+          if (!filt) {
+            token = pick;
+            done = true;
+            break;
+          }
+          const float ek = at(pick);
+          const uint32_t kk = __float_as_uint(ek);
+          float above = 0.f, before = 0.f;
+          for (int i = lane; i < V; i += 32) {
+            const float ev = at(i);
+            const uint32_t k = __float_as_uint(ev);
+            above += k > kk ? ev : 0.f;
+            before += (k == kk && i < pick) ? 1.f : 0.f;
+          }
+          above = warp_sum(above);
+          before = warp_sum(before);
+          if (above + before * ek < target) {
+            token = pick;
+            done = true;
+          }
+        }
+      }
+      if (done) {
+        // nothing left to do
+      } else if (filt) {
+        const float target = fmaxf(top_p, 1e-30f) * Z;
+        uint32_t lo = 0u, hi = 0x3f800000u;  // mass above lo >= target, mass above hi = 0 < target
+        while (hi - lo > 1u) {
+          const uint32_t mid = lo + ((hi - lo) >> 1);
+          float s = 0.f;
+          uint32_t kmn = 0xffffffffu, kmx = 0u;
+          for (int i = lane; i < V; i += 32) {
+            const float ev = at(i);
+            const uint32_t k = __float_as_uint(ev);
+            if (k > lo && k <= hi) {
+              kmn = min(kmn, k);
+              kmx = max(kmx, k);
+            }
+            s += k > mid ? ev : 0.f;
+          }
+          s = warp_sum(s);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            kmn = min(kmn, __shfl_xor_sync(0xffffffffu, kmn, o));
+            kmx = max(kmx, __shfl_xor_sync(0xffffffffu, kmx, o));
+          }
+          if (kmn == kmx) {  // a single key value is left in (lo, hi]: it is the boundary
+            hi = kmn;
+            break;
+          }
+          if (s < target) hi = mid; else lo = mid;
+        }
+        uint32_t kmin = 0xffffffffu;
+        for (int i = lane; i < V; i += 32) {
+          const uint32_t k = __float_as_uint(at(i));
+          if (k >= hi) kmin = min(kmin, k);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
+        key_b = kmin;
+        float above = 0.f, cnt = 0.f;
+        for (int i = lane; i < V; i += 32) {
+          const float ev = at(i);
+          const uint32_t k = __float_as_uint(ev);
+          above += k > key_b ? ev : 0.f;
+          cnt += k == key_b ? 1.f : 0.f;
+        }
+        above = warp_sum(above);
+        cnt = warp_sum(cnt);
+        int keep = (int)ceilf((target - above) / __uint_as_float(key_b));
+        keep = max(1, min(keep, (int)cnt));
+        if (keep < (int)cnt) {  // id of the keep-th token (in id order) whose key equals key_b
+          __syncwarp();  // chunks below were written by other lanes
+          int mine = 0;
+          for (int i = c0; i < c1; ++i) mine += __float_as_uint(at(i)) == key_b ? 1 : 0;
+          int incl = mine;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+          }
+          const int excl = incl - mine;
+          int found = V - 1;
+          const bool own = excl < keep && keep <= incl;
+          if (own) {
+            int seen = excl;
+            for (int i = c0; i < c1; ++i)
+              if (__float_as_uint(at(i)) == key_b && ++seen == keep) {
+                found = i;
+                break;
+              }
+          }
+          const unsigned who = __ballot_sync(0xffffffffu, own);
+          i_cut = __shfl_sync(0xffffffffu, found, who ? __ffs(who) - 1 : 0);
+        }
+      }
+      // exact path: inverse-CDF draw in token order over the kept tokens
+      if (!done) {
+      __syncwarp();  // chunks below were written by other lanes
+      const float inv_t = 1.f / temperature;
+      float mine = 0.f;
+      int last_kept = -1;
+      for (int i = c0; i < c1; ++i) {
+        const float ev = at(i);
+        bool kept = true;
+        if (filt) {
+          const uint32_t k = __float_as_uint(ev);
+          kept = k > key_b || (k == key_b && i <= i_cut);
+        }
+        const float w = !kept ? 0.f : (temperature == 1.f ? ev : __expf(__logf(ev) * inv_t));
+        at(i) = w;
+        mine += w;
+        if (kept) last_kept = i;
+      }
+      float incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      const float W = __shfl_sync(0xffffffffu, incl, 31);
+      const float excl = incl - mine;
+
+      const uint32_t bits = philox4x32_10((uint32_t)traj, (uint32_t)((unsigned long long)traj >> 32),
+                                          (uint32_t)(step + step_base), (uint32_t)kAttempts, seed_lo, seed_hi);
+      const float u = (float)(bits >> 8) * (1.0f / 16777216.0f);
+      const float tgt = u * W;
+      const bool own = mine > 0.f && excl <= tgt && tgt < incl;
+      int pick = last_kept;
+      if (own) {
+        const float local = tgt - excl;
+        float c = 0.f;
+        for (int i = c0; i < c1; ++i) {
+          const float w = at(i);
+          c += w;
+          if (w > 0.f && c > local) {
+            pick = i;
+            break;
+          }
+        }
+      }
+      const unsigned who = __ballot_sync(0xffffffffu, own);
+      if (who) token = __shfl_sync(0xffffffffu, pick, __ffs(who) - 1);
+      }
+    }
+  }
+  if (lane == 0) {
+    out_tok[r] = token;
+    if (out_mask) out_mask[r] = mask;
+    if (hist_tok) hist_tok[(long long)r * hist_stride + step] = token;
+    if (hist_mask) hist_mask[(long long)r * hist_stride + step] = mask;
+  }
+}
+
 template <typename T, int MODE>
 static int sample_launch(const void* logits, long long stride, int R, int V, float cap, float temperature, float top_p,
                          uint64_t seed, long long traj_id0, const long long* traj_ids, int step_base,
                          const int* step_ptr, const int* force, int force_rows, long long force_stride, int* out_tok,
                          int* out_mask, int* hist_tok, int* hist_mask, long long hist_stride, void* filtered, long long filt_stride,
                          cudaStream_t st) {
+  if (MODE == kModeSample && V <= 12000) {  // warp-per-row kernel: four rows of exp() values per CTA
+    const size_t wsmem = (size_t)kWarpRows * (V + 33) * sizeof(float);
+    int chunk = 1, log2c = 0;
+    while (chunk * 32 < V) {
+      chunk <<= 1;
+      ++log2c;
+    }
+    auto wk = sample_warp_kernel<T>;
+    if (wsmem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(wk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wsmem);
+      if (e != cudaSuccess) {
+        set_error("sample: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        return DGPT_E_CUDA;
+      }
+    }
+    wk<<<(R + kWarpRows - 1) / kWarpRows, 32 * kWarpRows, wsmem, st>>>(
+        static_cast<const T*>(logits), stride, R, V, log2c, cap, temperature, top_p, (uint32_t)seed,
+        (uint32_t)(seed >> 32), traj_id0, traj_ids, step_base, step_ptr, force, force_rows, force_stride, out_tok,
+        out_mask, hist_tok, hist_mask, hist_stride);
+    return launch_status("sample");
+  }
   const size_t smem = (size_t)V * 2 * sizeof(float);
   auto kern = sample_kernel<T, MODE>;
   if (smem > 48 * 1024) {
