@@ -21,7 +21,6 @@ namespace tc {
 constexpr int kBM = 128;          // queries per CTA
 constexpr int kBN = 128;          // keys per tile
 constexpr int kTmemCols = 256;    // S/P: [0,128), O tile: [128, 128 + D)
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait here
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -35,25 +34,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
+#ifdef DGPT_TC_TESTWAIT
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-// Bounded wait: false if the phase did not complete within kWaitLimitNs.
+// Waits are bounded in SM clock cycles (clock64 is a cheap register read; the global nanosecond timer is
+// not, and must stay out of the fast path).  4e9 cycles is about two seconds.
+constexpr long long kWaitLimitCycles = 4000000000ll;
+// Bounded wait: false if the phase did not complete within the limit.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  const unsigned long long t0 = global_ns();
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
   for (;;) {
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 32; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_ns() - t0 > kWaitLimitNs) return false;
+    if (clock64() - t0 > kWaitLimitCycles) return false;
   }
 }
 
@@ -203,15 +205,16 @@ struct Params {
 };
 
 // Bounded wait that also gives up early when another thread has raised the CTA's abort flag.
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  const unsigned long long t0 = global_ns();
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site = 2) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
   for (;;) {
-    for (int i = 0; i < 64; ++i)
+    for (int i = 0; i < 32; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (global_ns() - t0 > kWaitLimitNs) break;
+    if (clock64() - t0 > kWaitLimitCycles) break;
   }
-  *abort_flag = 1;
+  *abort_flag = site;  // which wait gave up (reported through the status word)
   return false;
 }
 
@@ -471,6 +474,363 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
 }
 
+// ---- warp-specialised variant ------------------------------------------------------------------
+// 128 softmax threads (one per query row), one warp whose first lane issues every tcgen05.mma and one warp
+// whose first lane issues every TMA load.  Scores and probabilities are double-buffered in TMEM (S0, S1 at columns 0 and 128; P0, P1 as
+// packed bf16 at 256 and 320; O at 384), K and V tiles live in two-deep rings, and all hand-offs are mbarriers:
+//   bar_s[b]  S of a tile is in buffer b            (tcgen05.commit)
+//   bar_p[b]  all 128 rows have written P into b    (128 thread arrivals)
+//   bar_o[b]  the P V product of that tile is done   (tcgen05.commit)
+// so the softmax of tile j overlaps P V of tile j-1 and Q K^T of tile j+1.  One CTA per SM (512 TMEM columns).
+#ifdef DGPT_TC_PROF
+__device__ long long g_prof[16];
+#define PROF_T(k) const long long prof_t##k = clock64()
+#define PROF_ADD(i, a, b) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 33 || tid == 128)) g_prof[i] += prof_t##b - prof_t##a; } while (0)
+#else
+#define PROF_T(k)
+#define PROF_ADD(i, a, b)
+#endif
+constexpr int kWsThreads = 192;
+constexpr uint32_t kWsTmemCols = 512;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(kWsThreads, 1)
+fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                  const __grid_constant__ CUtensorMap mv, const Params p) {
+  constexpr int kSub = D / 64;
+  constexpr uint32_t kSubBytes = kBN * 128;
+  constexpr uint32_t kTileBytes = kSub * kSubBytes;
+  constexpr uint32_t kIdescS = instr_desc(kBN, false);
+  constexpr uint32_t kIdescPV = instr_desc(D, true);
+  constexpr uint32_t kPCol = 256;  // P buffer b: columns [256 + 64 b, +64)
+  constexpr uint32_t kOCol = 384;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sV = smem + 4 * kTileBytes;  // Q | K0 K1 K2 | V0 V1   (K is needed a tile earlier than V: deeper ring)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t aQ = smem_u32(smem), aK = aQ + kTileBytes, aV = aQ + 4 * kTileBytes;
+  const uint32_t bar_q = smem_u32(bars);
+  const uint32_t bar_k0 = bar_q + 8, bar_v0 = bar_q + 32, bar_s0 = bar_q + 48, bar_p0 = bar_q + 64, bar_o0 = bar_q + 80,
+                 bar_kf0 = bar_q + 96;  // K slot released (its S product has been computed)
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int b = blockIdx.z, h = blockIdx.y;
+  const int qt = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int q0 = qt * kBM;
+  const int klen = p.kv_len ? p.kv_len[b] : p.kv_len_all;
+  const int kmax = p.causal ? min(klen, p.q_offset + min(q0 + kBM, p.Tq)) : klen;
+  const int n_tiles = kmax > 0 ? (kmax + kBN - 1) / kBN : 0;
+  const int pt = p.page_tokens;
+
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bar_q, 1);
+    mbar_init(bar_k0 + 16, 1);
+    for (int i = 0; i < 3; ++i) mbar_init(bar_kf0 + 8 * i, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_k0 + 8 * i, 1);
+      mbar_init(bar_v0 + 8 * i, 1);
+      mbar_init(bar_s0 + 8 * i, 1);
+      mbar_init(bar_p0 + 8 * i, kBM);
+      mbar_init(bar_o0 + 8 * i, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_async_smem();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(tmem_slot), kWsTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  bool fail = false;
+
+  if (warp == 5) {
+    // ================= loader: every TMA load (one lane) =================
+    if ((tid & 31) == 0 && n_tiles > 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&mq)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&mk)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&mv)) : "memory");
+      auto load_kv = [&](const CUtensorMap* map, uint32_t dst, uint32_t bar, int j) {
+        const int t0 = j * kBN;
+        if (pt >= kBN) {
+          const int lp = t0 / pt, in = t0 - lp * pt;
+          const int pg = p.page_table ? p.page_table[(long long)b * p.max_pages + lp] : b;
+          mbar_expect_tx(bar, kTileBytes);
+#pragma unroll
+          for (int s = 0; s < kSub; ++s) tma_load_4d(dst + s * kSubBytes, map, bar, s * 64, in, h, pg);
+        } else {
+          const int per = kBN / pt;
+          int valid = 0;
+          for (int q = 0; q < per; ++q) valid += (t0 + q * pt < klen) ? 1 : 0;
+          mbar_expect_tx(bar, (uint32_t)valid * pt * 128u * kSub);
+          for (int q = 0; q < valid; ++q) {
+            const int lp = t0 / pt + q;
+            const int pg = p.page_table ? p.page_table[(long long)b * p.max_pages + lp] : b;
+#pragma unroll
+            for (int s = 0; s < kSub; ++s) tma_load_4d(dst + s * kSubBytes + q * pt * 128, map, bar, s * 64, 0, h, pg);
+          }
+        }
+      };
+      int last_k[3] = {-1, -1, -1}, last_v[2] = {-1, -1};  // parity of the newest load per ring slot (for the drain on failure)
+      mbar_expect_tx(bar_q, kTileBytes);
+#pragma unroll
+      for (int s = 0; s < kSub; ++s) tma_load_4d(aQ + s * kSubBytes, &mq, bar_q, s * 64, h, q0, b);
+      for (int i = 0; i < 3 && i < n_tiles; ++i) {
+        load_kv(&mk, aK + i * kTileBytes, bar_k0 + 8 * i, i);
+        last_k[i] = 0;
+        if (i < 2) {
+          load_kv(&mv, aV + i * kTileBytes, bar_v0 + 8 * i, i);
+          last_v[i] = 0;
+        }
+      }
+      bool ok = true;
+      for (int j = 0; ok && j + 2 < n_tiles; ++j) {  // refill the rings behind the consumers
+        const int buf = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        if (j + 3 < n_tiles) {
+          // K slot j % 3 is free for tile j+3 once S_j has been computed.  The loader may run far behind the
+          // issuer, so it waits on a barrier of its own that completes once per use of the slot (bar_s could
+          // complete twice before the loader looks, which a parity wait cannot tell from "not yet").
+          const int ks = j % 3;
+          ok = wait_or_abort(bar_kf0 + 8 * ks, (uint32_t)((j / 3) & 1), abort_flag, 16);
+          if (!ok) break;
+          load_kv(&mk, aK + ks * kTileBytes, bar_k0 + 8 * ks, j + 3);
+          last_k[ks] = ((j + 3) / 3) & 1;
+        }
+        ok = wait_or_abort(bar_o0 + 8 * buf, ph, abort_flag, 17);  // P_j V_j is done: V slot j % 2 is free for tile j+2
+        if (!ok) break;
+        load_kv(&mv, aV + buf * kTileBytes, bar_v0 + 8 * buf, j + 2);
+        last_v[buf] = (int)(ph ^ 1u);
+      }
+      if (!ok || *abort_flag) {  // something ran out of time: give the copies still in flight a bounded chance to land
+        if (p.status) atomicExch(p.status, *abort_flag ? *abort_flag : 2);
+        mbar_wait(bar_q, 0);
+        for (int i = 0; i < 3; ++i)
+          if (last_k[i] >= 0) mbar_wait(bar_k0 + 8 * i, (uint32_t)last_k[i]);
+        for (int i = 0; i < 2; ++i)
+          if (last_v[i] >= 0) mbar_wait(bar_v0 + 8 * i, (uint32_t)last_v[i]);
+      }
+    }
+  } else if (warp == 4) {
+    // ================= MMA issuer (one lane) =================
+    if ((tid & 31) == 0 && n_tiles > 0) {
+      constexpr int kStepsS = D / 16, kStepsPV = kBN / 16;
+      auto issue_s = [&](int buf, int kslot) {  // S(buf) = Q K(kslot)^T
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < kStepsS; ++ks) {
+          const uint32_t off = (uint32_t)(ks >> 2) * kSubBytes + (uint32_t)(ks & 3) * 32u;
+          umma_ss(tmem + buf * 128, smem_desc(aQ + off, 16, 1024), smem_desc(aK + kslot * kTileBytes + off, 16, 1024),
+                  kIdescS, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(bar_s0 + 8 * buf);
+        umma_commit(bar_kf0 + 8 * kslot);
+      };
+      int last_s[2] = {-1, -1}, last_o[2] = {-1, -1};  // parity of the newest commit per buffer (for the drain on failure)
+      bool ok = wait_or_abort(bar_q, 0, abort_flag, 18);
+      for (int i = 0; ok && i < 2 && i < n_tiles; ++i) {
+        ok = wait_or_abort(bar_k0 + 8 * i, 0, abort_flag, 19);
+        if (ok) {
+          issue_s(i, i);
+          last_s[i] = 0;
+        }
+      }
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const int buf = j & 1;
+        const uint32_t ph = (uint32_t)((j >> 1) & 1);
+        const bool next_s = j + 2 < n_tiles;
+        // P_j is complete when every row has arrived; by then every row has also consumed S_j, so the same
+        // buffer can take S_{j+2} at once (P lives in its own columns)
+        PROF_T(10);
+        ok = wait_or_abort(bar_p0 + 8 * buf, ph, abort_flag, 20);
+        PROF_T(11);
+        ok = ok && wait_or_abort(bar_v0 + 8 * buf, ph, abort_flag, 21);
+        if (ok && next_s) ok = wait_or_abort(bar_k0 + 8 * ((j + 2) % 3), (uint32_t)(((j + 2) / 3) & 1), abort_flag, 22);
+        if (!ok) break;
+        PROF_T(12);
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < kStepsPV; ++ks)
+          umma_ts(tmem + kOCol, tmem + kPCol + buf * 64 + ks * 8,
+                  smem_desc(aV + buf * kTileBytes + ks * 2048, kSubBytes, 1024), kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(bar_o0 + 8 * buf);
+        last_o[buf] = (int)ph;
+        if (next_s) {
+          issue_s(buf, (j + 2) % 3);
+          last_s[buf] = (int)(ph ^ 1u);
+        }
+        PROF_T(13);
+        PROF_ADD(6, 10, 11);
+        PROF_ADD(7, 11, 12);
+        PROF_ADD(8, 12, 13);
+      }
+      if (!ok) {
+        if (!*abort_flag) *abort_flag = 2;
+        if (p.status) atomicExch(p.status, *abort_flag ? *abort_flag : 2);
+        for (int i = 0; i < 2; ++i) {
+          if (last_s[i] >= 0) mbar_wait(bar_s0 + 8 * i, (uint32_t)last_s[i]);
+          if (last_o[i] >= 0) mbar_wait(bar_o0 + 8 * i, (uint32_t)last_o[i]);
+        }
+      }
+    }
+  } else {
+    // ================= softmax threads: one query row each =================
+    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    float m = -INFINITY, l = 0.f;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int buf = j & 1;
+      const uint32_t ph = (uint32_t)((j >> 1) & 1);
+      const int t0 = j * kBN;
+      PROF_T(0);
+      // exits are taken by whole warps (the vote makes the decision uniform), never by single lanes
+      if (!__all_sync(0xffffffffu, wait_or_abort(bar_s0 + 8 * buf, ph, abort_flag, 23))) {
+        fail = true;
+        break;
+      }
+      tc_fence_after();
+      const int valid_rows = klen - t0;
+      if (valid_rows < kBN) {  // CTA-uniform: last, partial tile
+        if (!__all_sync(0xffffffffu, wait_or_abort(bar_v0 + 8 * buf, ph, abort_flag, 24))) {
+          fail = true;
+          break;
+        }
+        if (tid >= valid_rows) {  // value rows past the end may hold anything: clear them so that 0 * x stays 0
+#pragma unroll
+          for (int s = 0; s < kSub; ++s) {
+            uint4* vrow = reinterpret_cast<uint4*>(sV + buf * kTileBytes + s * kSubBytes + tid * 128);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+          }
+          fence_async_smem();
+        }
+      }
+      const bool need_mask = (t0 + kBN > klen) || (p.causal && t0 + kBN - 1 > p.q_offset + q0);
+      const int last_key = p.causal ? min(klen - 1, p.q_offset + q0 + tid) : klen - 1;
+      float sv[kBN];
+#pragma unroll
+      PROF_T(1);
+      for (int c = 0; c < 4; ++c) tmem_ld32_nowait(lane_addr + buf * 128 + c * 32, &sv[c * 32]);
+      tc_wait_ld();
+      PROF_T(2);
+      float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < kBN; ++i) {
+          sv[i] = (t0 + i <= last_key) ? sv[i] : -INFINITY;
+          mxs[i & 3] = fmaxf(mxs[i & 3], sv[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < kBN; ++i) mxs[i & 3] = fmaxf(mxs[i & 3], sv[i]);
+      }
+      const float mx2 = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * p.scale_log2;
+      float alpha = 1.f;  // lazy rescale: the running maximum only moves when exceeded by 2^8
+      if (mx2 > m + 8.f || m == -INFINITY) {
+        alpha = (m == -INFINITY) ? 0.f : ex2(m - mx2);
+        m = mx2;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // O may only be touched when no P V product is in flight: tile j-1's must have finished
+        // (tile j's cannot start before this row has arrived on bar_p below)
+        const bool ok = wait_or_abort(bar_o0 + 8 * (buf ^ 1), (uint32_t)(((j - 1) >> 1) & 1), abort_flag, 25);
+        if (!__all_sync(0xffffffffu, ok)) {
+          fail = true;
+          break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          float v[32];
+          tmem_ld32(lane_addr + kOCol + c * 32, v);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] *= alpha;
+          tmem_st32(lane_addr + kOCol + c * 32, v);
+        }
+      }
+      const float m_use = (m == -INFINITY) ? 0.f : m;
+      PROF_T(3);
+      float rs[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ex2(fmaf(sv[c * 32 + i], p.scale_log2, -m_use));  // -inf -> 0
+          const float p1 = ex2(fmaf(sv[c * 32 + i + 1], p.scale_log2, -m_use));
+          rs[(i >> 1) & 3] += p0 + p1;
+          const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+        }
+        tmem_st16(lane_addr + kPCol + buf * 64 + c * 16, packed);
+      }
+      l = l * alpha + ((rs[0] + rs[1]) + (rs[2] + rs[3]));
+      PROF_T(4);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar_p0 + 8 * buf);
+      PROF_T(5);
+      PROF_ADD(0, 0, 1);
+      PROF_ADD(1, 1, 2);
+      PROF_ADD(2, 2, 3);
+      PROF_ADD(3, 3, 4);
+      PROF_ADD(4, 4, 5);
+#ifdef DGPT_TC_PROF
+      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 33) g_prof[5] += 1;
+#endif
+    }
+    // every warp leaves the loop as a whole (waits are on CTA-wide events), so the collective loads below are safe
+    if (!fail && n_tiles > 0) {
+      const int last = n_tiles - 1;
+      if (!wait_or_abort(bar_o0 + 8 * (last & 1), (uint32_t)((last >> 1) & 1), abort_flag, 26)) fail = true;
+      tc_fence_after();
+    }
+    if (!__any_sync(0xffffffffu, fail)) {
+      const int qi = q0 + tid;
+      const bool row_ok = qi < p.Tq;
+      const float inv = (l > 0.f && n_tiles > 0) ? 1.f / l : 0.f;
+      const long long off = (long long)b * p.o_bs + (long long)qi * p.o_rs + (long long)h * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float v[32];
+        if (n_tiles > 0) {
+          tmem_ld32(lane_addr + kOCol + c * 32, v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0.f;
+        }
+        if (row_ok) {
+          if (p.o_f32) {
+            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.o) + off + c * 32);
+#pragma unroll
+            for (int d = 0; d < 32; d += 4)
+              dst[d >> 2] = make_float4(v[d] * inv, v[d + 1] * inv, v[d + 2] * inv, v[d + 3] * inv);
+          } else {
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.o) + off + c * 32;
+#pragma unroll
+            for (int d = 0; d < 32; d += 8) st16<__nv_bfloat16>(dst + d, v + d, inv);
+          }
+        }
+      }
+      if (row_ok && p.lse) p.lse[((long long)b * p.Tq + qi) * p.H + h] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
+    } else if (p.status) {
+      atomicExch(p.status, *abort_flag ? *abort_flag : 2);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kWsTmemCols);
+}
+
 // ---- host side -------------------------------------------------------------------------
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -513,6 +873,16 @@ static bool encode_map(CUtensorMap* map, const void* base, const cuuint64_t (&di
 }
 
 }  // namespace tc
+
+#ifdef DGPT_TC_PROF
+extern "C" int dgpt_debug_prof(long long* out, int reset) {
+  if (reset) {
+    long long z[16] = {0};
+    return (int)cudaMemcpyToSymbol(tc::g_prof, z, sizeof(z));
+  }
+  return (int)cudaMemcpyFromSymbol(out, tc::g_prof, 16 * sizeof(long long));
+}
+#endif
 
 bool fmha_tc_supported(const FmhaArgs& a, const dgpt_kv_layout& kv) {
   if (a.dtype != DGPT_BF16 || (a.D != 64 && a.D != 128)) return false;
@@ -568,6 +938,25 @@ int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
   size_t smem = (size_t)3 * (D / 64) * kBN * 128 + 64 + 1024;
   if (smem < 80 * 1024) smem = 80 * 1024;
   cudaError_t e;
+#ifndef DGPT_TC_NO_WS
+  {
+    // warp-specialised kernel: Q + two K + two V tiles, padded so that one CTA owns an SM (it allocates all 512 TMEM columns)
+    size_t ws_smem = (size_t)6 * (D / 64) * kBN * 128 + 256 + 1024;
+    if (ws_smem < 120 * 1024) ws_smem = 120 * 1024;
+    if (D == 64) {
+      e = cudaFuncSetAttribute(fmha_tc_ws_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ws_smem);
+      if (e == cudaSuccess) fmha_tc_ws_kernel<64><<<grid, kWsThreads, ws_smem, st>>>(mq, mk, mv, p);
+    } else {
+      e = cudaFuncSetAttribute(fmha_tc_ws_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ws_smem);
+      if (e == cudaSuccess) fmha_tc_ws_kernel<128><<<grid, kWsThreads, ws_smem, st>>>(mq, mk, mv, p);
+    }
+    if (e != cudaSuccess) {
+      set_error("fmha_tc: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return DGPT_E_CUDA;
+    }
+    return launch_status("fmha_tc_ws");
+  }
+#endif
   if (D == 64) {
     e = cudaFuncSetAttribute(fmha_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess) fmha_tc_kernel<64><<<grid, 128, smem, st>>>(mq, mk, mv, p);
