@@ -54,6 +54,7 @@ class DecodeRun:
         page_tokens: int = 64,
         use_graph: bool = True,
         fmha_impl: int = 0,
+        kv_pool: torch.Tensor | None = None,
     ) -> None:
         self.model = model
         emb = model.token_embedding_table.weight
@@ -77,7 +78,7 @@ class DecodeRun:
         device_prompts = prompts if isinstance(prompts, torch.Tensor) else None  # [S, P] int32, already on the GPU
         lens = [int(device_prompts.shape[1])] * S if device_prompts is not None else [len(p) for p in prompts]
         self.prompt_lens = lens
-        self.cache = PagedKVCache(L, H, D, S, N, max(lens), G, dt, dev, page_tokens=page_tokens)
+        self.cache = PagedKVCache(L, H, D, S, N, max(lens), G, dt, dev, page_tokens=page_tokens, pool=kv_pool)
         self.prefix_lens = torch.tensor(lens, dtype=torch.int32, device=dev)
         row_len = self.prefix_lens.repeat_interleave(N)
         self.tokens = torch.zeros(self.R, dtype=torch.int32, device=dev)

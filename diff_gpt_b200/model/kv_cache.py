@@ -115,6 +115,7 @@ class PagedKVCache:
         dtype: torch.dtype,
         device: torch.device | str,
         page_tokens: int = 64,
+        pool: torch.Tensor | None = None,
     ) -> None:
         pt = page_tokens
         self.page_tokens = pt
@@ -126,7 +127,12 @@ class PagedKVCache:
         self.own_pages = max(1, -(-max_new // pt))
         self.max_new = max_new
         n_pages = n_series * self.prefix_pages + self.n_rows * self.own_pages
-        self.pool = torch.empty((n_layer, n_pages, 2, n_head, pt, head_dim), dtype=dtype, device=device)
+        shape = (n_layer, n_pages, 2, n_head, pt, head_dim)
+        if pool is not None:  # storage handed in by the caller (e.g. kept across calls); contents need not be cleared
+            assert tuple(pool.shape) == shape and pool.dtype == dtype and pool.is_contiguous(), "pool does not fit this cache"
+            self.pool = pool
+        else:
+            self.pool = torch.empty(shape, dtype=dtype, device=device)
         pre = torch.arange(n_series * self.prefix_pages, dtype=torch.int32).view(n_series, self.prefix_pages)
         own = n_series * self.prefix_pages + torch.arange(self.n_rows * self.own_pages, dtype=torch.int32).view(
             self.n_rows, self.own_pages
