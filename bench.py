@@ -215,6 +215,8 @@ def run_ours(args) -> None:
     from diff_gpt_b200.dist import gather_trajectories
     from diff_gpt_b200.model.engine import DecodeRun
 
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: rank 0 prints exactly one JSON line
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -327,6 +329,10 @@ def run_ours(args) -> None:
     if world > 1:
         barrier()
 
+    prefill = None if args.no_prefill else prefill_attention(world, rank, dev)
+    if world > 1:
+        barrier()
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         prompt = prompts[0]
@@ -350,11 +356,77 @@ def run_ours(args) -> None:
                 "achieved_gbs_per_gpu": value / world * bytes_per_token / 1e9,
                 "frac_of_peak": value / world * bytes_per_token / 1e9 / pk["hbm_gbs"], "peak_source": pk["source"],
             },
-            "kernels": kernels, "status_ok": status_ok,
+            "prefill_attention": prefill, "kernels": kernels, "status_ok": status_ok,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def prefill_attention(world: int, rank: int, dev, lengths=(4096, 8192, 16384, 32768)) -> list:
+    """BASELINE config 5: one attention layer (RoPE + QK-norm + causal attention + output projection) on
+    Q, K, V ~ N(0, 1), 16 heads of 128, batch 8 split over the ranks; TFLOP/s counts 2 B H S^2 D for the attention kernel."""
+    import torch.distributed as dist
+
+    from diff_gpt_b200 import ops
+
+    B, H, D = max(1, 8 // world), 16, 128
+    C = H * D
+    pk = peaks()
+    g = torch.Generator(device=dev).manual_seed(5 + rank)
+    wp = (torch.randn((C, C), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    out = []
+    for S in lengths:
+        j = torch.arange(0, D, 2, dtype=torch.float32, device=dev) / D
+        ang = torch.outer(torch.arange(S, dtype=torch.float32, device=dev), 1.0 / (10000.0 ** j))
+        table = torch.stack([ang.cos(), ang.sin()], dim=-1).to(torch.bfloat16).contiguous()
+        qkv = torch.randn((B * S, 3 * C), device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
+        cache = torch.empty((B, 2, H, S, D), device=dev, dtype=torch.bfloat16)
+        lay = ops.kv_layout(cache[0, 0], cache[0, 1], 2 * H * S * D, S * D, S)
+        q_rot = torch.empty((B * S, C), device=dev, dtype=torch.bfloat16)
+        y = torch.empty_like(q_rot)
+        proj = torch.empty_like(q_rot)
+        zero = torch.zeros(B, dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+
+        def layer(timed: bool):
+            if timed:
+                ev[0].record()
+            ops.rope_qknorm_kvappend(qkv[:, :C], qkv[:, C : 2 * C], qkv[:, 2 * C :], q_rot, table, lay, zero, zero, None,
+                                     B, S, H, D, status)
+            if timed:
+                ev[1].record()
+            ops.fmha_prefill(q_rot, lay, y, B=B, H=H, Tq=S, D=D, q_batch_stride=S * C, q_row_stride=C,
+                             o_batch_stride=S * C, o_row_stride=C, kv_len_all=S, causal=True, impl=2, status=status)
+            if timed:
+                ev[2].record()
+            torch.mm(y, wp.t(), out=proj)
+            if timed:
+                ev[3].record()
+
+        layer(False)
+        layer(False)
+        torch.cuda.synchronize(dev)
+        t_attn, t_layer = [], []
+        for _ in range(3):
+            layer(True)
+            torch.cuda.synchronize(dev)
+            t_attn.append(ev[1].elapsed_time(ev[2]))
+            t_layer.append(ev[0].elapsed_time(ev[3]))
+        assert int(status.item()) == 0, "the attention kernel reported a device-side failure"
+        ta, tl = min(t_attn), min(t_layer)
+        if world > 1:
+            t = torch.tensor([ta, tl], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ta, tl = float(t[0]), float(t[1])
+        flops = 2.0 * B * world * H * S * S * D
+        out.append({"S": S, "batch": B * world, "attn_ms": ta, "layer_ms": tl, "attn_tflops": flops / ta / 1e9,
+                    "attn_tflops_per_gpu": flops / ta / 1e9 / world,
+                    "frac_of_bf16_peak": flops / ta / 1e9 / world / pk["bf16_tflops"], "peak": pk["bf16_tflops"],
+                    "peak_source": pk["source"]})
+        del qkv, cache, q_rot, y, proj
+    return out
 
 
 def roofline(kernels: dict, rows: int, n_series: int) -> dict:
@@ -473,6 +545,7 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-kernel-pass", action="store_true", help="skip the per-kernel timing step")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the config-5 prefill-attention sweep")
     ap.add_argument("--no-graph", action="store_true", help="launch the decode steps eagerly (for profilers)")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: 2048 trajectories x 64 steps (4.8 GB of KV), same model and prompt")

@@ -1,0 +1,87 @@
+"""Reduced-size versions of the BASELINE configurations 2, 3 and 5 against the CPU oracle (same code paths as full size)."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_decode, ref_math
+
+pytestmark = pytest.mark.gpu
+
+
+def _gpu_model(shape, w, dtype):
+    from diff_gpt_b200 import GPT
+
+    m = GPT(vocab_size=shape.vocab_size, n_embd=shape.n_embd, block_size=shape.block_size, n_head=shape.n_head,
+            n_layer=shape.n_layer).eval()
+    sd = dict(w)
+    sd["lm_head.weight"] = sd["token_embedding_table.weight"]
+    m.load_state_dict(sd)
+    return m.to(dtype).cuda()
+
+
+def test_config2_shape_batched_forward_bf16_head_dim_32():
+    """Config 2 narrowed (n_embd 128, 4 heads of 32, 2 layers, vocab 512, T = 96, batch 6): full causal forward
+    with soft-cap in bf16 through the warp-level attention kernel; logits within 2e-2 of the oracle."""
+    shape = ref_math.Shape(vocab_size=512, n_embd=128, n_head=4, n_layer=2, block_size=96)
+    w = ref_math.random_weights(shape, seed=2, dtype=torch.bfloat16, std=0.08)
+    idx = torch.randint(0, 512, (6, 96), generator=torch.Generator().manual_seed(2))
+    want = ref_math.forward(shape, w, idx).float()
+    got = _gpu_model(shape, w, torch.bfloat16)(idx.cuda())[0].float().cpu()
+    assert got.shape == (6, 96, 512)
+    assert (got - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+
+
+def test_config3_shape_many_series_one_trajectory_teacher_forced():
+    """Config 3 narrowed: 5 series x 1 trajectory, 7 channels of which 2 are forced from a schedule, head_dim 64.
+    One trajectory per series takes the per-row path with the prompt split along the keys (no shared-prompt phase).
+    fp32 so that argmax streams can be compared token for token with the oracle."""
+    from diff_gpt_b200 import Engine, TemperatureSampler
+
+    shape = ref_math.Shape(vocab_size=128, n_embd=128, n_head=2, n_layer=2, block_size=1024)
+    w = ref_math.random_weights(shape, seed=3, dtype=torch.float32, std=0.2)
+    g = torch.Generator().manual_seed(3)
+    F, P, G = 7, 7 * 90, 7 * 6  # prompt long enough (630 keys) for the split-K policy to engage
+    prompts = [torch.randint(0, 128, (P,), generator=g).tolist() for _ in range(5)]
+    cov = [torch.randint(0, 128, (G,), generator=g).tolist() for _ in range(5)]
+    scheds = [[c[p] if (p % F) >= 5 else None for p in range(G)] for c in cov]
+    eng = Engine(_gpu_model(shape, w, torch.float32))
+    toks, masks = eng.generate_many(prompts, 1, G, TemperatureSampler(0.0), force_schedules=scheds)
+    assert toks.shape == (5, 1, G)
+    for s in range(5):
+        ref, ref_m, _ = ref_decode.mc_decode(shape, w, prompts[s], 1, G, temperature=0.0, force_schedule=scheds[s])
+        assert toks[s, 0].cpu().tolist() == ref[0].tolist(), s
+        assert masks[s, 0].cpu().tolist() == ref_m[0].tolist()
+
+
+@pytest.mark.parametrize("S", [200, 384])
+def test_config5_shape_attention_layer_bf16_head_dim_128(S):
+    """Config 5 narrowed (batch 2, 4 heads of 128, S = 200 / 384): RoPE + QK-norm + causal attention on the
+    tcgen05 kernel + output projection, inputs injected after the projections; within 2e-2 of the oracle."""
+    from diff_gpt_b200 import ops
+
+    B, H, D = 2, 4, 128
+    C = H * D
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, H, D, generator=g).to(torch.bfloat16)
+    wp = (torch.randn(C, C, generator=g) * 0.02).to(torch.bfloat16)
+    table = ref_math.rope_table(D, 512).to(torch.bfloat16)
+    want = ref_math.attention_only(q, k, v, table, wp).float()
+
+    cap = -(-S // 128) * 128
+    cache = torch.zeros(B, 2, H, cap, D, dtype=torch.bfloat16, device="cuda")
+    lay = ops.kv_layout(cache[0, 0], cache[0, 1], 2 * H * cap * D, cap * D, cap)
+    qkv = torch.cat([q.reshape(B * S, C), k.reshape(B * S, C), v.reshape(B * S, C)], dim=1).cuda()
+    q_rot = torch.empty(B * S, C, dtype=torch.bfloat16, device="cuda")
+    zero = torch.zeros(B, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.rope_qknorm_kvappend(qkv[:, :C], qkv[:, C : 2 * C], qkv[:, 2 * C :], q_rot, table.cuda(), lay, zero, zero, None,
+                             B, S, H, D, status)
+    y = torch.empty(B * S, C, dtype=torch.bfloat16, device="cuda")
+    ops.fmha_prefill(q_rot, lay, y, B=B, H=H, Tq=S, D=D, q_batch_stride=S * C, q_row_stride=C, o_batch_stride=S * C,
+                     o_row_stride=C, kv_len_all=S, causal=True, impl=2, status=status)
+    out = torch.mm(y, wp.cuda().t()).view(B, S, C).float().cpu()
+    assert status.item() == 0
+    assert (out - want).abs().max().item() <= 2e-2 * want.abs().max().item()
