@@ -244,16 +244,25 @@ def run_ours(args) -> None:
     def series_of(step_idx: int) -> list[int]:
         return [(step_idx * series_per_step + j) % N_SERIES for j in range(series_per_step)]
 
-    kv_pool = None  # the 38.7 GB page pool is allocated by the first step and handed to the following ones
+    # The 38.7 GB page pool, the forward plans and the captured decode-step graph depend only on the shape
+    # of a step: they are built by the first step and reused by the following ones (what a server that
+    # decodes one batch after another keeps alive between requests).
+    kv_pool = None
+    runs: dict[bool, DecodeRun] = {}
 
     def device_step(step_idx: int, use_graph: bool = not args.no_graph, gather: bool = True):
         nonlocal kv_pool
         ids = series_of(step_idx)
-        run = DecodeRun(
-            model, prompts_dev[torch.tensor(ids, device=dev)], n_local, HORIZON, sampler, 42, None,
-            traj_offset=rank * n_local, series_offset=ids[0], use_graph=use_graph, kv_pool=kv_pool,
-        )
-        kv_pool = run.cache.pool
+        batch = prompts_dev[torch.tensor(ids, device=dev)]
+        run = runs.get(use_graph)
+        if run is None:
+            run = runs[use_graph] = DecodeRun(
+                model, batch, n_local, HORIZON, sampler, 42, None, traj_offset=rank * n_local, series_offset=ids[0],
+                use_graph=use_graph, kv_pool=kv_pool, overlap_prefix=not args.no_overlap,
+            )
+            kv_pool = run.cache.pool
+        else:
+            run.load(batch, None, traj_offset=rank * n_local, series_offset=ids[0])
         run.start()
         run.advance(HORIZON)
         toks = run.history.view(series_per_step, n_local, HORIZON)
@@ -274,8 +283,7 @@ def run_ours(args) -> None:
     statuses = []
     for i in range(args.steps):
         out, run = device_step(args.warmup + i)
-        statuses.append(run.plan.status)  # device-side status words, read after the timed region
-        del run
+        statuses.append(run.plan.status.clone())  # device-side status words, read after the timed region
     e1.record()
     barrier()
     launches = _lib.stats.launches
@@ -459,12 +467,14 @@ def roofline(kernels: dict, rows: int, n_series: int) -> dict:
             "traffic": None, "launches": k["launches"], "avg_launch_ms": k["avg_ms"]}
 
 
-def kernel_case(name: str, iters: int = 5) -> None:
+def kernel_case(name: str, iters: int = 8) -> None:
     """One kernel alone on a case sized for an `ncu --set full` capture (a few launches, < 2 GB touched).
 
     decode_attn: config-4 shapes at decode step 128 — 4096 trajectories x 12 heads, head_dim 64, 128 own
                  tokens per trajectory in 64-token pages, prompt partial merged, gate applied.
     fmha:        config-5 shapes at S = 4096 — batch 8, 16 heads, head_dim 128, causal, dense K/V.
+    sample:      config-4 logits, 4096 rows x 4096 tokens, nucleus 0.9.
+    depthmix:    config-4 rows, 8 candidates (mid-stack).
     Prints one JSON line with the CUDA-event time per launch and the achieved rate.
     """
     from diff_gpt_b200 import ops
@@ -517,15 +527,37 @@ def kernel_case(name: str, iters: int = 5) -> None:
 
         work = R * V * 2
         unit, peak = "GB/s", pk["hbm_gbs"]
+    elif name == "depthmix":
+        # config-4 shapes in the middle of the stack: 4096 rows x 768 channels, 8 candidates.  Four sets of
+        # candidates (201 MB) are rotated so that consecutive launches do not find their inputs in L2.
+        R, C, n_c, sets = TRAJECTORIES, CFG4["n_embd"], 8, 4
+        cands = [[torch.randn((R, C), device=dev, dtype=torch.bfloat16, generator=g) for _ in range(n_c)] for _ in range(sets)]
+        wmix = torch.randn((C,), device=dev, dtype=torch.bfloat16, generator=g) * 0.1
+        out = torch.empty((R, C), device=dev, dtype=torch.bfloat16)
+        turn = [0]
+
+        def launch():
+            ops.depthmix(cands[turn[0] % sets], wmix, None, out)
+            turn[0] += 1
+
+        work = R * C * 2 * (n_c + 1)
+        unit, peak = "GB/s", pk["hbm_gbs"]
     else:
         raise SystemExit(f"unknown kernel case {name}")
     for _ in range(3):
         launch()
     torch.cuda.synchronize()
+    # The launches are replayed from a CUDA graph so that the time is the device's, not the host's
+    # (a Python call costs more than some of these kernels run).
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(iters):
+            launch()
+    graph.replay()
+    torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    for _ in range(iters):
-        launch()
+    graph.replay()
     b.record()
     torch.cuda.synchronize()
     ms = a.elapsed_time(b) / iters
@@ -536,7 +568,7 @@ def kernel_case(name: str, iters: int = 5) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel-case", default=None, choices=["decode_attn", "fmha", "sample"],
+    ap.add_argument("--kernel-case", default=None, choices=["decode_attn", "fmha", "sample", "depthmix"],
                     help="run one kernel alone on a small case (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
@@ -546,6 +578,8 @@ def main() -> None:
     ap.add_argument("--no-kernel-pass", action="store_true", help="skip the per-kernel timing step")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the config-5 prefill-attention sweep")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="run the shared-prompt attention phase before the per-row phase instead of beside it")
     ap.add_argument("--no-graph", action="store_true", help="launch the decode steps eagerly (for profilers)")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: 2048 trajectories x 64 steps (4.8 GB of KV), same model and prompt")

@@ -4,7 +4,7 @@ Mirrors the reference's import surface for this path:
 
     from diff_gpt_b200 import GPT, KVCache, Engine, TemperatureSampler, NucleusSampler
 
-The CUDA library (libdgpt_b200.so, built by `python -m diff_gpt_b200.build`) is
+The CUDA library (libdgpt_b200.so, built by `python diff_gpt_b200/build.py`) is
 required at import time; there is no CPU or PyTorch fallback.
 """
 

@@ -60,6 +60,8 @@ PROTOTYPES = {
         C.c_int,
         [_p, _i64, _kvp, _p, _p, _p, _p, _p, _p, _p, _i64, _p, _i64, _p, _sz, _i32, _i32, _i32, _i32, _i32, _p],
     ),
+    "dgpt_decode_attn_partial": (C.c_int, [_p, _i64, _kvp, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _p]),
+    "dgpt_attn_merge": (C.c_int, [_p, _p, _p, _p, _p, _i64, _p, _i64, _i32, _i32, _i32, _i32, _p]),
     "dgpt_decode_attn_static_capacity_bytes": (_sz, []),
     "dgpt_decode_attn_static": (
         C.c_int,
@@ -168,7 +170,7 @@ class _Lib:
 def _load() -> _Lib:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m diff_gpt_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python diff_gpt_b200/build.py` "
             "(there is no fallback implementation)"
         )
     return _Lib(C.CDLL(LIB_PATH))

@@ -1,6 +1,8 @@
 """Compile the CUDA sources under csrc/ into libdgpt_b200.so (sm_100a only).
 
-    python -m diff_gpt_b200.build [--force] [--verbose]
+    python diff_gpt_b200/build.py [--force] [--verbose]
+
+Run it as a script: the package itself refuses to import until the library exists.
 
 nvcc cross-compiles without a GPU.  Objects are cached next to the sources and
 rebuilt when a source or header is newer; the shared object lands in this

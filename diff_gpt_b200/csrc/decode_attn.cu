@@ -48,8 +48,8 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
                    const int* __restrict__ start1, const int* __restrict__ len1, const int* __restrict__ step_ptr,
                    const float* __restrict__ prefix_o, const float* __restrict__ prefix_lse,
                    const T* __restrict__ gate, long long gate_stride, T* __restrict__ y, long long y_stride,
-                   float* __restrict__ ws_ml, float* __restrict__ ws_o, int n_splits, int R, int H,
-                   float scale_log2) {
+                   float* __restrict__ ws_ml, float* __restrict__ ws_o, float* __restrict__ part_o,
+                   float* __restrict__ part_lse, int n_splits, int R, int H, float scale_log2) {
   using Cfg = DecodeCfg<T, D>;
   constexpr int VEC = Cfg::VEC, LPT = Cfg::LPT, TPW = Cfg::TPW;
   const long long rh = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -60,7 +60,7 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
   const int split = blockIdx.y;
   const int step = step_ptr ? *step_ptr : 0;
   const bool have_prefix = prefix_lse != nullptr;
-  const int n0 = have_prefix ? 0 : len0[r];
+  const int n0 = (have_prefix || len0 == nullptr) ? 0 : len0[r];
   const int s1 = start1[r];
   const int n = n0 + len1[r] + step;
   int chunk = (n + n_splits - 1) / n_splits;
@@ -164,6 +164,16 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
       *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
     return;
   }
+  if (part_lse) {  // normalised partial over this row's keys; the caller merges it with another partial later
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    if (e == 0) part_lse[rh] = l > 0.f ? (m + log2f(l)) * (1.f / kLog2e) : -INFINITY;
+    float* dst = part_o + rh * D + e * VEC;
+#pragma unroll
+    for (int i = 0; i < VEC; i += 4)
+      *reinterpret_cast<float4*>(dst + i) =
+          make_float4(acc[i] * inv, acc[i + 1] * inv, acc[i + 2] * inv, acc[i + 3] * inv);
+    return;
+  }
   if (have_prefix) {
     const float mp = prefix_lse[rh] * kLog2e;  // normalised partial: l = 1
     float po[VEC];
@@ -222,11 +232,58 @@ __global__ void decode_combine_kernel(const float* __restrict__ ws_ml, const flo
   Io<T>::st(y + (long long)r * y_stride + (long long)h * D + d, out);
 }
 
+// Merge of two normalised partials (o, lse) per (row, head), then the sigmoid gate; one thread per 16 bytes of y.
+template <typename T>
+__global__ void attn_merge_kernel(const float* __restrict__ oa, const float* __restrict__ lsea,
+                                  const float* __restrict__ ob, const float* __restrict__ lseb,
+                                  const T* __restrict__ gate, long long gate_stride, T* __restrict__ y,
+                                  long long y_stride, int R, int H, int D) {
+  constexpr int VEC = Io<T>::kVec16;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long RH = (long long)R * H;
+  const int DV = D / VEC;
+  if (idx >= RH * DV) return;
+  const long long rh = idx / DV;
+  const int d = (int)(idx - rh * DV) * VEC;
+  const int r = (int)(rh / H), h = (int)(rh - (long long)r * H);
+  const float ma = lsea[rh], mb = lseb[rh];
+  const float m = fmaxf(ma, mb);
+  float wa = 0.f, wb = 0.f;
+  if (m != -INFINITY) {
+    wa = __expf(ma - m);  // exp(-inf) = 0 for an empty side
+    wb = __expf(mb - m);
+    const float inv = 1.f / (wa + wb);
+    wa *= inv;
+    wb *= inv;
+  }
+  float out[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; i += 4) {
+    const float4 a = *reinterpret_cast<const float4*>(oa + rh * D + d + i);
+    const float4 b = *reinterpret_cast<const float4*>(ob + rh * D + d + i);
+    out[i] = a.x * wa + b.x * wb;
+    out[i + 1] = a.y * wa + b.y * wb;
+    out[i + 2] = a.z * wa + b.z * wb;
+    out[i + 3] = a.w * wa + b.w * wb;
+  }
+  const long long col = (long long)h * D + d;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) out[i] = Io<T>::round(out[i]);
+  if (gate) {
+    float gf[VEC];
+    ld16<T>(gate + (long long)r * gate_stride + col, gf);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) out[i] *= Io<T>::round(1.f / (1.f + __expf(-gf[i])));
+  }
+  st16<T>(y + (long long)r * y_stride + col, out, 1.f);
+}
+
 template <typename T, int D>
 static int decode_launch(const void* q, long long q_stride, const KvView& kv, const int* len0, const int* start1,
                          const int* len1, const int* step_ptr, const float* prefix_o, const float* prefix_lse,
                          const void* gate, long long gate_stride, void* y, long long y_stride, float* ws,
-                         int n_splits, int R, int H, cudaStream_t st) {
+                         int n_splits, int R, int H, cudaStream_t st, float* part_o = nullptr,
+                         float* part_lse = nullptr) {
   const long long RH = (long long)R * H;
   float* ws_ml = ws;
   float* ws_o = ws ? ws + 2 * RH * n_splits : nullptr;
@@ -234,7 +291,8 @@ static int decode_launch(const void* q, long long q_stride, const KvView& kv, co
   dim3 grid((unsigned)((RH + 3) / 4), (unsigned)n_splits);
   decode_attn_kernel<T, D><<<grid, 128, 0, st>>>(static_cast<const T*>(q), q_stride, kv, len0, start1, len1, step_ptr,
                                                  prefix_o, prefix_lse, static_cast<const T*>(gate), gate_stride,
-                                                 static_cast<T*>(y), y_stride, ws_ml, ws_o, n_splits, R, H, scale_log2);
+                                                 static_cast<T*>(y), y_stride, ws_ml, ws_o, part_o, part_lse, n_splits,
+                                                 R, H, scale_log2);
   if (int e = launch_status("decode_attn")) return e;
   if (n_splits > 1) {
     const long long n = RH * D;
@@ -300,6 +358,71 @@ extern "C" int dgpt_decode_attn(const void* q, int64_t q_row_stride, const dgpt_
 #undef DGPT_DEC
   set_error("decode_attn: dtype %d with head_dim %d is not built", dtype, D);
   return DGPT_E_UNSUPPORTED;
+}
+
+// ---- the two halves of dgpt_decode_attn as separate launches ---------------------------------------
+// The shared-prompt contraction and the per-row pass are independent until the merge, so a caller may
+// run them on two streams; the merge waits for both.
+extern "C" int dgpt_decode_attn_partial(const void* q, int64_t q_row_stride, const dgpt_kv_layout* kv,
+                                        const int32_t* len0, const int32_t* start1, const int32_t* len1,
+                                        const int32_t* step_ptr, float* part_o, float* part_lse, int32_t R,
+                                        int32_t H, int32_t D, int32_t dtype, void* stream) {
+  DGPT_REQUIRE(q && part_o && part_lse && start1 && len1, "decode_attn_partial: NULL pointer");
+  DGPT_REQUIRE(R >= 0 && H > 0, "decode_attn_partial: bad sizes");
+  DGPT_REQUIRE(q_row_stride % 8 == 0, "decode_attn_partial: row strides must be multiples of 8 elements");
+  if (int e = validate_kv(kv, D)) return e;
+  if (R == 0) return DGPT_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const KvView view = make_view(kv);
+#define DGPT_DEC(TT, DD)                                                                                           \
+  return decode_launch<TT, DD>(q, q_row_stride, view, len0, start1, len1, step_ptr, nullptr, nullptr, nullptr, 0, \
+                               nullptr, 0, nullptr, 1, R, H, st, part_o, part_lse)
+  if (dtype == DGPT_F32) {
+    switch (D) {
+      case 8: DGPT_DEC(float, 8);
+      case 16: DGPT_DEC(float, 16);
+      case 32: DGPT_DEC(float, 32);
+      case 64: DGPT_DEC(float, 64);
+      case 128: DGPT_DEC(float, 128);
+    }
+  } else if (dtype == DGPT_BF16) {
+    switch (D) {
+      case 8: DGPT_DEC(__nv_bfloat16, 8);
+      case 16: DGPT_DEC(__nv_bfloat16, 16);
+      case 32: DGPT_DEC(__nv_bfloat16, 32);
+      case 64: DGPT_DEC(__nv_bfloat16, 64);
+      case 128: DGPT_DEC(__nv_bfloat16, 128);
+      case 256: DGPT_DEC(__nv_bfloat16, 256);
+    }
+  }
+#undef DGPT_DEC
+  set_error("decode_attn_partial: dtype %d with head_dim %d is not built", dtype, D);
+  return DGPT_E_UNSUPPORTED;
+}
+
+extern "C" int dgpt_attn_merge(const float* o_a, const float* lse_a, const float* o_b, const float* lse_b,
+                               const void* gate, int64_t gate_row_stride, void* y, int64_t y_row_stride, int32_t R,
+                               int32_t H, int32_t D, int32_t dtype, void* stream) {
+  DGPT_REQUIRE(o_a && lse_a && o_b && lse_b && y, "attn_merge: NULL pointer");
+  DGPT_REQUIRE(R >= 0 && H > 0 && D > 0 && D % 8 == 0, "attn_merge: head_dim must be a multiple of 8");
+  DGPT_REQUIRE(y_row_stride % 8 == 0 && gate_row_stride % 8 == 0,
+               "attn_merge: row strides must be multiples of 8 elements");
+  if (R == 0) return DGPT_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long n = (long long)R * H * (D / (dtype == DGPT_F32 ? 4 : 8));
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == DGPT_F32) {
+    attn_merge_kernel<float><<<blocks, 256, 0, st>>>(o_a, lse_a, o_b, lse_b, static_cast<const float*>(gate),
+                                                     gate_row_stride, static_cast<float*>(y), y_row_stride, R, H, D);
+  } else if (dtype == DGPT_BF16) {
+    attn_merge_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(o_a, lse_a, o_b, lse_b,
+                                                             static_cast<const __nv_bfloat16*>(gate), gate_row_stride,
+                                                             static_cast<__nv_bfloat16*>(y), y_row_stride, R, H, D);
+  } else {
+    set_error("attn_merge: dtype %d is not built", dtype);
+    return DGPT_E_UNSUPPORTED;
+  }
+  return launch_status("attn_merge");
 }
 
 // ---- split-K decode attention for callers that cannot allocate ------------------------------------

@@ -129,8 +129,9 @@ __global__ void depthmix_kernel(CandPtrs cands, int n_cands, const T* __restrict
 // Same algorithm with 16-byte accesses: lane l owns vectors l + 32*i (i < NV) of VEC elements each.
 // Used when n_embd is a multiple of VEC and every pointer is 16-byte aligned.
 template <typename T, int NV>
-__global__ void depthmix_vec_kernel(CandPtrs cands, int n_cands, const T* __restrict__ w, T* __restrict__ out_h,
-                                    T* __restrict__ out_rn, long long rows, int C) {
+__global__ void __launch_bounds__(128, 4)
+depthmix_vec_kernel(CandPtrs cands, int n_cands, const T* __restrict__ w, T* __restrict__ out_h,
+                    T* __restrict__ out_rn, long long rows, int C) {
   constexpr int VEC = Io<T>::kVec16;
   constexpr int E = NV * VEC;
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -146,54 +147,76 @@ __global__ void depthmix_vec_kernel(CandPtrs cands, int n_cands, const T* __rest
     if (n_cands > 1 && j < nvec) ld16<T>(w + j * VEC, wv + i * VEC);
   }
   float m = -INFINITY, l = 0.f;
-  // The candidates are reduced one after another (online softmax), so the next candidate's row is
+  // The candidates are reduced one after another (online softmax), so the rows of the next ones are
   // fetched (as raw 16-byte words) before the current one is reduced, to keep loads in flight.
-  uint4 nxt[NV];
-  auto fetch = [&](int n) {
+#ifndef DGPT_MIX_AHEAD
+#define DGPT_MIX_AHEAD 1  // candidates in flight beyond the current one (2 and 3 measured slower)
+#endif
+  constexpr int AHEAD = DGPT_MIX_AHEAD;
+  uint4 nxt[AHEAD][NV];
+  auto fetch = [&](int n, uint4* dst) {
     const T* src = static_cast<const T*>(cands.p[n]) + row * C;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int j = lane + 32 * i;
-      nxt[i] = j < nvec ? *reinterpret_cast<const uint4*>(src + j * VEC) : make_uint4(0u, 0u, 0u, 0u);
+      dst[i] = j < nvec ? *reinterpret_cast<const uint4*>(src + j * VEC) : make_uint4(0u, 0u, 0u, 0u);
     }
   };
-  fetch(0);
+#pragma unroll
+  for (int a = 0; a < AHEAD; ++a)
+    if (a < n_cands) fetch(a, nxt[a]);
   for (int n = 0; n < n_cands; ++n) {
     float v[E];
-    float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < NV; ++i) unpack16<T>(nxt[i], v + i * VEC);
-    if (n + 1 < n_cands) fetch(n + 1);
+    for (int i = 0; i < NV; ++i) unpack16<T>(nxt[0][i], v + i * VEC);
 #pragma unroll
-    for (int x = 0; x < E; ++x) ss += v[x] * v[x];
+    for (int a = 0; a + 1 < AHEAD; ++a) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) nxt[a][i] = nxt[a + 1][i];
+    }
+    if (n + AHEAD < n_cands) fetch(n + AHEAD, nxt[AHEAD - 1]);
     if (n_cands == 1) {
 #pragma unroll
       for (int x = 0; x < E; ++x) acc[x] = v[x];
       l = 1.f;
       break;
     }
-    ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)C + kRmsEps);
-    float dot = 0.f;
+    // logit = rms_norm(v) . w = rsqrt(mean(v^2) + eps) * (v . w): both sums in one sweep and one
+    // interleaved butterfly.  (The reference rounds rms_norm(v) to the storage type before the
+    // product; for bf16 that changes the logit by ~1e-4 of its own rounding step.)
+    float s4[4] = {0.f, 0.f, 0.f, 0.f}, d4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int x = 0; x < E; ++x) dot += Io<T>::round(v[x] * inv) * wv[x];
-    dot = Io<T>::round(warp_sum(dot));
-    const float m_new = fmaxf(m, dot);
-    const float resc = __expf(m - m_new);
-    const float pw = __expf(dot - m_new);
-    l = l * resc + pw;
+    for (int x = 0; x < E; ++x) {
+      s4[x & 3] += v[x] * v[x];
+      d4[x & 3] += v[x] * wv[x];
+    }
+    float ss = (s4[0] + s4[1]) + (s4[2] + s4[3]), dr = (d4[0] + d4[1]) + (d4[2] + d4[3]);
 #pragma unroll
-    for (int x = 0; x < E; ++x) acc[x] = acc[x] * resc + pw * v[x];
-    m = m_new;
+    for (int o = 16; o > 0; o >>= 1) {
+      ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      dr += __shfl_xor_sync(0xffffffffu, dr, o);
+    }
+    const float dot = Io<T>::round(dr * rsqrtf(ss / (float)C + kRmsEps));
+    if (dot > m) {  // warp-uniform: the accumulator is rescaled only when the running maximum moves
+      const float resc = __expf(m - dot);
+      l *= resc;
+#pragma unroll
+      for (int x = 0; x < E; ++x) acc[x] *= resc;
+      m = dot;
+    }
+    const float pw = __expf(dot - m);
+    l += pw;
+#pragma unroll
+    for (int x = 0; x < E; ++x) acc[x] += pw * v[x];
   }
   const float invl = 1.f / l;
-  float ss = 0.f;
+  float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int x = 0; x < E; ++x) {
     acc[x] = Io<T>::round(acc[x] * invl);
-    ss += acc[x] * acc[x];
+    s4[x & 3] += acc[x] * acc[x];
   }
-  ss = warp_sum(ss);
+  const float ss = warp_sum((s4[0] + s4[1]) + (s4[2] + s4[3]));
   const float inv = rsqrtf(ss / (float)C + kRmsEps);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {

@@ -38,7 +38,24 @@ def _effective_max_tokens(block_size: int, prompt_len: int, max_tokens: int | No
 
 
 class DecodeRun:
-    """State of one batched Monte-Carlo decode: S series x N trajectories, G steps."""
+    """State of one batched Monte-Carlo decode: S series x N trajectories, G steps.
+
+    Everything that depends only on the SHAPE of the job (page pool, tables, forward plans, the captured
+    decode-step graph) is built once; `load` brings in a new set of prompts of the same lengths and rewinds,
+    so a server decoding batch after batch of equally shaped requests pays for construction and graph
+    capture once.  `key` identifies the shape; two jobs with equal keys can share a DecodeRun.
+    """
+
+    @staticmethod
+    def key_for(model, prompt_lens, num_samples, max_tokens, sampler, seed, has_force, page_tokens, use_graph,
+                fmha_impl, overlap_prefix) -> tuple:
+        spec = (1.0, 1.0) if sampler is None else (sampler.native_spec() if isinstance(sampler, Sampler) else None)
+        emb = model.token_embedding_table.weight
+        return (
+            id(model), str(emb.device), emb.dtype, tuple(prompt_lens), num_samples, max_tokens, spec,
+            None if spec is not None else id(sampler), seed, has_force, page_tokens, use_graph, fmha_impl,
+            overlap_prefix,
+        )
 
     def __init__(
         self,
@@ -55,6 +72,7 @@ class DecodeRun:
         use_graph: bool = True,
         fmha_impl: int = 0,
         kv_pool: torch.Tensor | None = None,
+        overlap_prefix: bool = True,
     ) -> None:
         self.model = model
         emb = model.token_embedding_table.weight
@@ -75,49 +93,43 @@ class DecodeRun:
         self.temperature, self.top_p = spec if spec is not None else (1.0, 1.0)
         self.sampler = sampler
 
-        device_prompts = prompts if isinstance(prompts, torch.Tensor) else None  # [S, P] int32, already on the GPU
-        lens = [int(device_prompts.shape[1])] * S if device_prompts is not None else [len(p) for p in prompts]
+        on_device = isinstance(prompts, torch.Tensor)  # [S, P] int32, already on the GPU
+        lens = [int(prompts.shape[1])] * S if on_device else [len(p) for p in prompts]
         self.prompt_lens = lens
+        self.key = self.key_for(
+            model, lens, N, G, sampler, seed, force_schedules is not None, page_tokens, use_graph, fmha_impl,
+            overlap_prefix,
+        )
+        self.packed = model.packed_weights()  # the graph holds these tensors' addresses
         self.cache = PagedKVCache(L, H, D, S, N, max(lens), G, dt, dev, page_tokens=page_tokens, pool=kv_pool)
         self.prefix_lens = torch.tensor(lens, dtype=torch.int32, device=dev)
         row_len = self.prefix_lens.repeat_interleave(N)
         self.tokens = torch.zeros(self.R, dtype=torch.int32, device=dev)
         self.history = torch.zeros((self.R, max(G, 1)), dtype=torch.int32, device=dev)
         self.step = torch.zeros(1, dtype=torch.int32, device=dev)
-        ids = (torch.arange(S, dtype=torch.int64) + series_offset).repeat_interleave(N) * (1 << 32)
-        ids += (torch.arange(N, dtype=torch.int64) + traj_offset).repeat(S)
-        self.traj_ids = ids.to(dev)
+        self.traj_ids = torch.zeros(self.R, dtype=torch.int64, device=dev)
         self.force = None
         self.force_host = None
         if force_schedules is not None:
-            f = torch.tensor(
-                [[-1 if t is None else int(t) for t in sch[:G]] for sch in force_schedules], dtype=torch.int32
-            )
-            self.force_host = f
-            self.force = f.to(dev)
+            self.force = torch.zeros((S, G), dtype=torch.int32, device=dev)
 
-        # ---- prefill, grouped by prompt length; only the last position's logits are needed ----
+        # ---- prefill plans, one per distinct prompt length; only the last position's logits are needed ----
         self.logits0 = torch.empty((S, model.vocab_size), dtype=dt, device=dev)
         groups: dict[int, list[int]] = {}
         for s, n in enumerate(lens):
             groups.setdefault(n, []).append(s)
         zero = torch.zeros(S, dtype=torch.int32, device=dev)
+        self.prefills = []
         for P, members in groups.items():
-            table = self.cache.prefix_table[torch.tensor(members, device=dev)].contiguous()
+            idx = torch.tensor(members, device=dev)
+            table = self.cache.prefix_table[idx].contiguous()
             layouts = [self.cache._layout(l, table) for l in range(L)]
             bind = KvBinding(
                 layouts=layouts, pos0=zero[: len(members)], slot0=zero[: len(members)], kv_len=P, q_offset=0,
                 fmha_impl=fmha_impl,
             )
             plan = ForwardPlan(model, len(members), P, last_only=True)
-            if device_prompts is not None:
-                ids32 = device_prompts.reshape(-1)
-            else:
-                ids32 = torch.tensor([prompts[s] for s in members], dtype=torch.int32).reshape(-1).to(dev)
-            out = plan.run(ids32, bind)
-            self.logits0[torch.tensor(members, device=dev)] = out
-            self._keep = (table, layouts)  # keep the table alive until the work has been enqueued and run
-            del plan
+            self.prefills.append((P, members, idx, bind, plan, table))
 
         # ---- decode plan ----
         shared = N >= SHARED_PREFIX_MIN_ROWS
@@ -136,10 +148,47 @@ class DecodeRun:
             shared_len=self.prefix_lens if shared else None,
             rows_per_series=N,
             fmha_impl=fmha_impl,
+            overlap_prefix=overlap_prefix and shared,
         )
         self.plan = ForwardPlan(model, self.R, 1)
         self.graph = None
         self.done = 0  # tokens produced so far per row
+        self.rng = None
+        self.load(prompts, force_schedules, traj_offset, series_offset)
+
+    def reusable(self) -> bool:
+        """False once the model's weights have been repacked (the captured graph points at the old ones)."""
+        return self.model.packed_weights() is self.packed
+
+    def load(self, prompts, force_schedules=None, traj_offset: int = 0, series_offset: int = 0) -> None:
+        """Prefill a new set of prompts (same lengths as the first) and rewind to step 0."""
+        S, N, G, dev = self.S, self.N, self.G, self.dev
+        on_device = isinstance(prompts, torch.Tensor)
+        lens = [int(prompts.shape[1])] * len(prompts) if on_device else [len(p) for p in prompts]
+        assert lens == self.prompt_lens, "load() needs prompts of the lengths this run was built for"
+        assert (force_schedules is not None) == (self.force is not None)
+        ids = (torch.arange(S, dtype=torch.int64) + series_offset).repeat_interleave(N) * (1 << 32)
+        ids += (torch.arange(N, dtype=torch.int64) + traj_offset).repeat(S)
+        self.traj_ids.copy_(ids)
+        if force_schedules is not None:
+            f = torch.tensor(
+                [[-1 if t is None else int(t) for t in sch[:G]] for sch in force_schedules], dtype=torch.int32
+            )
+            self.force_host = f
+            self.force.copy_(f)
+        self.step.zero_()
+        self.plan.status.zero_()
+        for P, members, idx, bind, plan, _table in self.prefills:
+            if on_device:
+                ids32 = prompts.reshape(-1) if len(members) == S else prompts[idx].reshape(-1)
+            else:
+                ids32 = torch.tensor([prompts[s] for s in members], dtype=torch.int32).reshape(-1).to(dev)
+            out = plan.run(ids32, bind)
+            if len(members) == S:
+                self.logits0.copy_(out)
+            else:
+                self.logits0[idx] = out
+        self.done = 0
         self.rng = None
 
     # -- sampling ---------------------------------------------------------------------
@@ -231,6 +280,8 @@ class DecodeRun:
 
     def check_status(self) -> None:
         bad = int(self.plan.status.item())
+        for entry in self.prefills:
+            bad = bad or int(entry[4].status.item())
         if bad:
             raise RuntimeError(f"device-side status {bad}: a cache slot or position was out of range, or a bounded wait ran out")
 
@@ -239,10 +290,15 @@ class DecodeRun:
 
 
 class Engine:
-    __slots__ = "model"
+    __slots__ = ("model", "_run")
 
     def __init__(self, model: BaseGPT) -> None:
         self.model = model
+        self._run = None  # the last DecodeRun: reused when the next job has the same shape
+
+    def release(self) -> None:
+        """Drop the cached decode state (page pool, plans, captured graph)."""
+        self._run = None
 
     # ---- additive, device-level API -----------------------------------------------------
     @torch.inference_mode()
@@ -259,8 +315,13 @@ class Engine:
         page_tokens: int = 64,
         use_graph: bool = True,
         fmha_impl: int = 0,
+        overlap_prefix: bool = True,
     ) -> tuple[torch.Tensor, torch.Tensor]:
         """Decode every prompt `num_samples` times.
+
+        `prompts` is a list of token lists, or an int32 device tensor [S, P] of equally long prompts.
+        The decode state (page pool, plans, captured step graph) is kept on the engine and reused when the
+        next call has the same shape; `release()` frees it.
 
         Returns (tokens, masks): int32 device tensors of shape (S, num_samples, G); masks are 1 where a
         token was sampled and 0 where it was forced.  `traj_offset`/`series_offset` shift the ids that key
@@ -268,6 +329,8 @@ class Engine:
         """
         assert isinstance(self.model, GPT), "generate_many needs the diff_gpt_b200 GPT"
         assert len(prompts) > 0 and all(len(p) > 0 for p in prompts), "tokens must be non-empty"
+        if isinstance(prompts, torch.Tensor):
+            assert prompts.is_cuda and prompts.dtype == torch.int32 and prompts.dim() == 2 and prompts.is_contiguous()
         G = min(_effective_max_tokens(self.model.block_size, len(p), max_tokens) for p in prompts)
         S = len(prompts)
         dev = self.model.token_embedding_table.weight.device
@@ -280,13 +343,26 @@ class Engine:
                 assert len(sch) >= G, (
                     f"force_schedule must cover all generation steps (len={len(sch)} < {G})"
                 )
-        run = DecodeRun(
-            self.model, prompts, num_samples, G, sampler, seed, force_schedules, traj_offset=traj_offset,
-            series_offset=series_offset, page_tokens=page_tokens, use_graph=use_graph, fmha_impl=fmha_impl,
+        on_device = isinstance(prompts, torch.Tensor)
+        lens = [int(prompts.shape[1])] * S if on_device else [len(p) for p in prompts]
+        key = DecodeRun.key_for(
+            self.model, lens, num_samples, G, sampler, seed, force_schedules is not None, page_tokens, use_graph,
+            fmha_impl, overlap_prefix,
         )
+        run = self._run
+        if run is not None and run.key == key and run.reusable():
+            run.load(prompts, force_schedules, traj_offset, series_offset)
+        else:
+            self._run = run = None  # free the old pool before the new one is allocated
+            run = DecodeRun(
+                self.model, prompts, num_samples, G, sampler, seed, force_schedules, traj_offset=traj_offset,
+                series_offset=series_offset, page_tokens=page_tokens, use_graph=use_graph, fmha_impl=fmha_impl,
+                overlap_prefix=overlap_prefix,
+            )
+            self._run = run
         run.start()
         run.advance(G)
-        toks = run.history.view(S, num_samples, -1)[:, :, :G]
+        toks = run.history.view(S, num_samples, -1)[:, :, :G].clone()  # the run's buffer is reused by the next call
         if run.force is not None:
             masks = (run.force[:, None, :G] < 0).to(torch.int32).expand(S, num_samples, G).contiguous()
         else:

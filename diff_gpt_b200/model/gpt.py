@@ -133,6 +133,7 @@ class KvBinding:
     shared_len: torch.Tensor | None = None
     rows_per_series: int = 0
     fmha_impl: int = 0
+    overlap_prefix: bool = False  # run the shared-prompt phase on a second stream beside the per-row phase
 
 
 class ForwardPlan:
@@ -163,6 +164,9 @@ class ForwardPlan:
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.prefix_o = None
         self.prefix_lse = None
+        self.part_o = None
+        self.part_lse = None
+        self.side = None
         self.workspace = None
 
     def _decode_extras(self, b: KvBinding) -> None:
@@ -172,6 +176,10 @@ class ForwardPlan:
         if b.shared_layouts is not None and self.prefix_o is None:
             self.prefix_o = torch.empty((self.n, H, D), dtype=torch.float32, device=dev)
             self.prefix_lse = torch.empty((self.n, H), dtype=torch.float32, device=dev)
+        if b.shared_layouts is not None and b.overlap_prefix and b.n_splits == 1 and self.part_o is None:
+            self.part_o = torch.empty((self.n, H, D), dtype=torch.float32, device=dev)
+            self.part_lse = torch.empty((self.n, H), dtype=torch.float32, device=dev)
+            self.side = torch.cuda.Stream(device=dev, priority=-1)
         if b.n_splits > 1 and self.workspace is None:
             nbytes = ops.decode_attn_workspace_bytes(self.n, H, D, b.n_splits)
             self.workspace = torch.empty(nbytes // 4, dtype=torch.float32, device=dev)
@@ -207,16 +215,31 @@ class ForwardPlan:
                 po = pl = None
                 if b.shared_layouts is not None:
                     N = b.rows_per_series
-                    ops.fmha_prefill(
+                    prefix_phase = lambda: ops.fmha_prefill(  # noqa: E731
                         self.q, b.shared_layouts[i], self.prefix_o, B=n_seq // N, H=H, Tq=N, D=D,
                         q_batch_stride=N * C, q_row_stride=C, o_batch_stride=N * C, o_row_stride=C,
                         kv_len=b.shared_len, causal=False, lse=self.prefix_lse, impl=b.fmha_impl, status=self.status,
                     )
                     po, pl = self.prefix_o, self.prefix_lse
-                ops.decode_attn(
-                    self.q, b.layouts[i], b.len0, b.start1, b.len1, b.step, self.y, H=H, D=D, gate=gv,
-                    prefix_o=po, prefix_lse=pl, workspace=self.workspace, n_splits=b.n_splits,
-                )
+                if po is not None and self.side is not None:
+                    # The tensor-core contraction over the shared prompt and the HBM-bound pass over each
+                    # row's own tokens need different parts of the SM: run them side by side, then merge.
+                    main = torch.cuda.current_stream()
+                    self.side.wait_stream(main)
+                    with torch.cuda.stream(self.side):
+                        prefix_phase()
+                    ops.decode_attn_partial(
+                        self.q, b.layouts[i], None, b.start1, b.len1, b.step, self.part_o, self.part_lse, H=H, D=D
+                    )
+                    main.wait_stream(self.side)
+                    ops.attn_merge(po, pl, self.part_o, self.part_lse, self.y, H=H, D=D, gate=gv)
+                else:
+                    if po is not None:
+                        prefix_phase()
+                    ops.decode_attn(
+                        self.q, b.layouts[i], b.len0, b.start1, b.len1, b.step, self.y, H=H, D=D, gate=gv,
+                        prefix_o=po, prefix_lse=pl, workspace=self.workspace, n_splits=b.n_splits,
+                    )
             else:
                 ops.fmha_prefill(
                     self.q, b.layouts[i], self.y, B=n_seq, H=H, Tq=T, D=D, q_batch_stride=T * C, q_row_stride=C,

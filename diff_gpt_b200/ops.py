@@ -181,6 +181,54 @@ def decode_attn(
     )
 
 
+def decode_attn_partial(
+    q: torch.Tensor,
+    kv: KvLayout,
+    len0: torch.Tensor | None,
+    start1: torch.Tensor,
+    len1: torch.Tensor,
+    step: torch.Tensor | None,
+    part_o: torch.Tensor,
+    part_lse: torch.Tensor,
+    *,
+    H: int,
+    D: int,
+) -> None:
+    """Per-row half of `decode_attn`: normalised fp32 result and log-sum-exp, to be merged by `attn_merge`."""
+    _cuda(q, len0, start1, len1, step, part_o, part_lse)
+    assert part_o.dtype == torch.float32 and part_lse.dtype == torch.float32
+    assert part_o.is_contiguous() and part_lse.is_contiguous()
+    check(
+        lib.dgpt_decode_attn_partial(
+            q.data_ptr(), q.stride(0), C.byref(kv), _ptr(len0), start1.data_ptr(), len1.data_ptr(), _ptr(step),
+            part_o.data_ptr(), part_lse.data_ptr(), q.shape[0], H, D, dtype_code(q), _stream(),
+        )
+    )
+
+
+def attn_merge(
+    o_a: torch.Tensor,
+    lse_a: torch.Tensor,
+    o_b: torch.Tensor,
+    lse_b: torch.Tensor,
+    y: torch.Tensor,
+    *,
+    H: int,
+    D: int,
+    gate: torch.Tensor | None = None,
+) -> None:
+    """y = merge of two normalised attention partials, times sigmoid(gate)."""
+    _cuda(o_a, lse_a, o_b, lse_b, y, gate)
+    for t in (o_a, lse_a, o_b, lse_b):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    check(
+        lib.dgpt_attn_merge(
+            o_a.data_ptr(), lse_a.data_ptr(), o_b.data_ptr(), lse_b.data_ptr(), _ptr(gate),
+            0 if gate is None else gate.stride(0), y.data_ptr(), y.stride(0), y.shape[0], H, D, dtype_code(y), _stream(),
+        )
+    )
+
+
 def decode_attn_static_capacity_bytes() -> int:
     return int(lib.dgpt_decode_attn_static_capacity_bytes())
 

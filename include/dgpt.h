@@ -134,6 +134,23 @@ int dgpt_decode_attn(const void* q, int64_t q_row_stride, const dgpt_kv_layout* 
                      size_t workspace_bytes, int32_t n_splits, int32_t R, int32_t H, int32_t D,
                      int32_t dtype, void* stream);
 
+/* The two halves of dgpt_decode_attn as separate launches, for callers that run the shared-prompt
+ * contraction (dgpt_fmha_prefill with lse) and the per-row pass on two streams at once.
+ * dgpt_decode_attn_partial reduces cache slots [0, len0[r]) (skipped when len0 is NULL) and
+ * [start1[r], start1[r] + len1[r] + step) of sequence r and writes the normalised result
+ * part_o [R, H, D] fp32 with its natural-log sum of exponentials part_lse [R, H] fp32
+ * (-inf and zeros for a row without keys).
+ * dgpt_attn_merge combines two such partials, y = (e^lse_a o_a + e^lse_b o_b) / (e^lse_a + e^lse_b),
+ * rounds to `dtype` and multiplies by sigmoid(gate) when gate is non-NULL.
+ * Together they replace src/diff_gpt/model/mha.py:65-68 and :83-84 exactly as dgpt_decode_attn does. */
+int dgpt_decode_attn_partial(const void* q, int64_t q_row_stride, const dgpt_kv_layout* kv,
+                             const int32_t* len0, const int32_t* start1, const int32_t* len1,
+                             const int32_t* step_ptr, float* part_o, float* part_lse, int32_t R,
+                             int32_t H, int32_t D, int32_t dtype, void* stream);
+int dgpt_attn_merge(const float* o_a, const float* lse_a, const float* o_b, const float* lse_b,
+                    const void* gate, int64_t gate_row_stride, void* y, int64_t y_row_stride, int32_t R,
+                    int32_t H, int32_t D, int32_t dtype, void* stream);
+
 /* dgpt_decode_attn for callers that cannot allocate device memory.  (No counterpart in the reference:
  * its attention never needs scratch memory.)
  * Who needs it: a host that must not call cudaMalloc where it launches — an inference server whose

@@ -238,6 +238,68 @@ def test_multi_series_batch_equals_single_series_runs():
     assert fm[0, 0].tolist() == [1, 0, 1, 1, 1, 1, 1, 1, 1] and fm[2, 0].tolist() == [1] * 9
 
 
+def test_engine_reuses_decode_state_across_calls_of_one_shape():
+    """A second call of the same shape reloads prompts into the cached pool, plans and graph; its tokens
+    equal those of a fresh engine, with and without teacher forcing, and after the weights changed."""
+    from diff_gpt_b200 import Engine, NucleusSampler, TemperatureSampler
+
+    g = load_golden("small_bf16_d32")
+    m = _model(g["meta"], golden_weights(g, torch.float32), torch.float32)
+    s = NucleusSampler(0.9, TemperatureSampler(1.1))
+    a = [g["idx"][0].tolist(), g["idx"][1].tolist()]
+    b = [g["idx"][2].tolist(), g["idx"][0].tolist()[::-1]]
+    eng = Engine(m)
+    first, _ = eng.generate_many(a, 20, 10, s, seed=5)
+    run = eng._run
+    second, _ = eng.generate_many(b, 20, 10, s, seed=5, series_offset=2, traj_offset=3)
+    assert eng._run is run and run.graph is not None  # same state, same captured graph
+    fresh, _ = Engine(m).generate_many(b, 20, 10, s, seed=5, series_offset=2, traj_offset=3)
+    assert torch.equal(second, fresh)
+    again, _ = eng.generate_many(a, 20, 10, s, seed=5)
+    assert torch.equal(again, first)
+    # forcing: schedules are reloaded too
+    sch1 = [[None, 4] + [None] * 8, [None] * 10]
+    sch2 = [[9] + [None] * 9, [None, None, 3] + [None] * 7]
+    eng.generate_many(a, 20, 10, s, seed=5, force_schedules=sch1)
+    run = eng._run
+    f2, m2 = eng.generate_many(b, 20, 10, s, seed=5, force_schedules=sch2)
+    assert eng._run is run
+    w2, wm2 = Engine(m).generate_many(b, 20, 10, s, seed=5, force_schedules=sch2)
+    assert torch.equal(f2, w2) and torch.equal(m2, wm2) and bool((f2[0, :, 0] == 9).all())
+    # another shape, or new weights, rebuild instead of replaying a stale graph
+    eng.generate_many(a, 20, 7, s, seed=5)
+    assert eng._run is not run
+    run = eng._run
+    with torch.no_grad():
+        m.token_embedding_table.weight.mul_(1.5)
+    changed, _ = eng.generate_many(a, 20, 7, s, seed=5)
+    assert eng._run is not run
+    want, _ = Engine(m).generate_many(a, 20, 7, s, seed=5)
+    assert torch.equal(changed, want)
+    eng.release()
+    assert eng._run is None
+
+
+def test_overlapped_prefix_phase_equals_sequential():
+    """Shared-prompt phase beside the per-row phase on a second stream (then a merge launch) against the
+    one-stream form whose per-row kernel merges in its epilogue: same tokens, eager and graph."""
+    from diff_gpt_b200 import Engine, TemperatureSampler
+
+    g = load_golden("small_bf16_d32")
+    w = golden_weights(g, torch.float32)
+    m = _model(g["meta"], w, torch.float32)
+    prompts = [g["idx"][0].tolist(), g["idx"][2].tolist()]
+    s = TemperatureSampler(0.0)
+    outs = []
+    for overlap in (False, True):
+        for graph in (False, True):
+            t, _ = Engine(m).generate_many(prompts, 24, 12, s, seed=1, overlap_prefix=overlap, use_graph=graph)
+            outs.append(t)
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    ref, _, _ = ref_decode.mc_decode(_shape(g["meta"]), w, prompts[0], 1, 12, temperature=0.0)
+    assert outs[3][0, 0].tolist() == ref[0].tolist()
+
+
 def test_python_callable_sampler_sees_device_logits():
     from diff_gpt_b200 import Engine
 

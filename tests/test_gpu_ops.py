@@ -63,6 +63,16 @@ def test_depthmix_golden_and_random(dtype, tol, tag):
         out = torch.empty(9, C, dtype=dtype, device="cuda")
         ops.depthmix([t.cuda() for t in cs], wv.cuda(), out, None)
         assert _rel(out, want) <= (2e-5 if dtype == torch.float32 else 3e-2), C
+    # candidate counts on both sides of the shared-memory-staged kernel's limit (32), odd row count
+    for n_c in (2, 3, 13, 17, 32, 33):
+        cs = [(torch.randn(11, 768, generator=gen) * (1 + 0.3 * i)).to(dtype) for i in range(n_c)]
+        wv = (torch.randn(768, generator=gen) * 0.2).to(dtype)
+        want = ref_math.depth_mix(cs, wv)
+        out = torch.empty(11, 768, dtype=dtype, device="cuda")
+        rn = torch.empty_like(out)
+        ops.depthmix([t.cuda() for t in cs], wv.cuda(), out, rn)
+        assert _rel(out, want) <= (2e-5 if dtype == torch.float32 else 3e-2), n_c
+        assert _rel(rn, ref_math.rms_norm(out.cpu())) <= tol * 8, n_c
 
 
 @pytest.mark.parametrize("dtype,tol,tag", DT)
@@ -257,6 +267,22 @@ def test_decode_attn_two_ranges(dtype, tol, tag, D, n_splits, with_prefix):
         att = ref_math.sdpa(qh, kk, vv, q_offset=10**6).transpose(1, 2).reshape(H * D)
         want = att * torch.sigmoid(gate[r])
         assert _rel(y[r], want) <= (2e-5 if dtype == torch.float32 else 1.5e-2), r
+    if n_splits > 1:
+        return
+    # the same result from the two-launch form: per-row partial, then merge with the other partial
+    part_o = torch.full((R, H, D), float("nan"), dtype=torch.float32, device="cuda")
+    part_lse = torch.full((R, H), float("nan"), dtype=torch.float32, device="cuda")
+    y2 = torch.empty_like(y)
+    if with_prefix:  # prompt partial from the prefill kernel, own tokens from the partial kernel
+        ops.decode_attn_partial(q.cuda(), lay_row, None, start1, len1, step, part_o, part_lse, H=H, D=D)
+        ops.attn_merge(po, pl, part_o, part_lse, y2, H=H, D=D, gate=gate.cuda())
+    else:  # both ranges in the partial kernel, merged with an empty partial
+        ops.decode_attn_partial(q.cuda(), lay_row, len0, start1, len1, step, part_o, part_lse, H=H, D=D)
+        zo = torch.zeros_like(part_o)
+        zl = torch.full_like(part_lse, float("-inf"))
+        ops.attn_merge(zo, zl, part_o, part_lse, y2, H=H, D=D, gate=gate.cuda())
+    assert torch.isfinite(part_lse).all()
+    assert _rel(y2, y) <= (2e-6 if dtype == torch.float32 else 8e-3)
 
 
 def _philox_u(seed: int, traj: int, step: int, attempt: int = 0) -> float:
