@@ -1,16 +1,27 @@
-// tcgen05 / TMEM prefill attention for bf16, head_dim 64 or 128 (sm_100a).
+// tcgen05 / TMEM attention for bf16, head_dim 64 or 128 (sm_100a): causal / chunk prefill, and the
+// shared-prompt phase of the Monte-Carlo decode (all trajectories of a series against the prompt K/V).
 //
-// One CTA of 128 threads owns a 128-query tile of one (batch, head); thread t owns
-// query row t, which is also TMEM lane t.  Per 128-key tile:
-//   TMA     Q once, K and V tiles (128-byte swizzled, one box per page and per 64-wide half of D)
-//   UMMA 1  S = Q K^T          -> TMEM columns [0,128) fp32           (tcgen05.mma, operands in smem)
-//   softmax rows read S with tcgen05.ld, exponentiate, write P as packed bf16 over S (tcgen05.st)
-//   UMMA 2  O_tile = P V       -> TMEM columns [128,128+D) fp32       (A = P from TMEM, B = V MN-major)
-//   rows add O_tile into fp32 register accumulators with the usual online-softmax rescale.
-// Two CTAs are resident per SM (256 TMEM columns and <= 97 KB of shared memory each), so one
-// CTA's softmax overlaps the other's tensor-core work.  No cluster launch and no multicast.
-// Every wait on an mbarrier is bounded; if one runs out the CTA records a status word, drains
-// what it issued, frees its TMEM and returns.
+// fmha_tc_ws_kernel (the one that runs): one CTA of 192 threads per 128-query tile of one (batch, head),
+// one CTA per SM, all 512 TMEM columns.  The warps have fixed roles:
+//   warp 5, lane 0  loader: TMA loads of Q (once) and of the K / V tiles (128-byte swizzle, one box per
+//                   page and per 64-wide half of D) into a ring of 3 K slots and 2 V slots
+//   warp 4, lane 0  issuer: S_j = Q K_j^T into one of two S buffers in TMEM, and O += P_j V_j with P read
+//                   from TMEM (A operand) and V MN-major; it issues P V for tile j, then S for tile j + 2,
+//                   so the tensor cores work on one tile while the softmax warps work on the next
+//   warps 0-3       softmax: thread t owns query row t = TMEM lane t; reads S with tcgen05.ld, keeps the
+//                   running maximum and sum, writes P as packed bf16 into one of two P buffers
+//                   (tcgen05.st) and rescales O in TMEM only when the maximum has moved by more than 2^8
+// TMEM columns: S0 [0,128)  S1 [128,256)  P0 [256,320)  P1 [320,384)  O [384, 384 + D).
+// mbarriers: Q loaded; K slot full x3 / free x3; V slot full x2; S ready x2; P ready x2 (128 arrivals);
+// P V done x2 (frees the P buffer and the V slot).  The K-free barriers are separate from S-ready so that
+// the loader can never run two phases ahead of a barrier it waits on.
+//
+// fmha_tc_kernel (built with -DDGPT_TC_NO_WS, kept as the simpler reference point): 128 threads, no
+// fixed roles, 256 TMEM columns and two CTAs per SM so that one CTA's softmax overlaps the other's MMAs.
+//
+// No cluster launch and no multicast.  Every wait on an mbarrier is bounded in clock cycles; if one runs
+// out the CTA stores the code of the waiting site in a status word, raises a CTA-wide abort flag so the
+// other roles stop waiting too, drains what it issued, frees its TMEM and returns.
 #include <cuda.h>
 
 #include "fmha.cuh"

@@ -201,8 +201,14 @@ int dgpt_step_advance(int32_t* step_ptr, int32_t delta, void* stream);
  *   nucleus  = tokens whose probability mass BEFORE them, in descending softmax(z) order, is < top_p
  *              (top_p >= 1 disables the filter, top_p <= 0 keeps only the top token; ties broken by lower id first)
  *   token    = argmax z over the nucleus                 if temperature == 0
- *            = inverse-CDF draw from softmax(z / temperature) over the nucleus, using one
- *              Philox4x32-10 uniform keyed by (seed, traj_id0 + row, step + step_base)
+ *            = a draw from softmax(z / temperature) restricted to the nucleus.  Uniforms come from
+ *              Philox4x32-10 with key = seed and counter = (traj id low, traj id high, step + step_base, a).
+ *              Rows of up to 12000 tokens draw by rejection: attempt a = 0..7 is an inverse-CDF draw over
+ *              ALL tokens, accepted if the token lies in the nucleus (accepted draws follow exactly the
+ *              restricted distribution); after 8 rejections, and for wider rows always, the nucleus boundary
+ *              is computed and one inverse-CDF draw is made inside it with a = 8 (wider rows: a = 0).
+ *              The stream is a function of (seed, traj id, step) only: it does not depend on the batch,
+ *              on the launch shape or on which GPU holds the row.
  *   f = force_schedule[(row / force_group_rows) * force_group_stride + step]   (one schedule per group of rows;
  *       stride 0 = one schedule for all);  if force_schedule && f >= 0: token = f, mask = 0, else mask = 1
  * step = *step_ptr (0 when NULL).  traj_ids (device int64 [R]) overrides traj_id0 + row when non-NULL.
