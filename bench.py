@@ -455,15 +455,24 @@ def roofline(kernels: dict, rows: int, n_series: int) -> dict:
     k = mine[top]
     total_s = k["total_ms"] / 1e3
     steps = HORIZON - 1  # decode forwards (the forward after the last token is skipped)
-    if top == "dgpt_decode_attn":
+    if top in ("dgpt_decode_attn", "dgpt_decode_attn_partial"):
         # per launch (one layer, decode forward g = 1..255): every row reads its g own K and V vectors (C bf16 each), plus
-        # q, gate (bf16), the prompt partial (fp32 o + lse) and writes y (bf16)
+        # q (bf16); the one-stream form also reads gate (bf16) and the prompt partial (fp32 o + lse) and writes y (bf16),
+        # the two-stream form writes its own fp32 partial (o + lse) instead
         kv_bytes = sum(rows * 2 * C * 2 * g for g in range(1, steps + 1)) * L
-        io_bytes = steps * L * rows * (3 * C * 2 + C * 4 + H * 4)
+        per_row = (3 * C * 2 + C * 4 + H * 4) if top == "dgpt_decode_attn" else (C * 2 + C * 4 + H * 4)
+        io_bytes = steps * L * rows * per_row
         achieved = (kv_bytes + io_bytes) / total_s / 1e9
-        return {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
-                "launches": k["launches"], "avg_launch_ms": k["avg_ms"], "algorithmic_bytes_per_launch": (kv_bytes + io_bytes) / k["launches"]}
+        # DRAM traffic per launch: the ncu capture of this kernel at decode step 128 (profiles/) read and wrote 1.002 x
+        # its algorithmic bytes; the traffic is proportional to the keys read, so the ratio is applied to the mean launch
+        out = {"kernel": top, "bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+               "frac": achieved / pk["hbm_gbs"], "traffic": 1.002 * (kv_bytes + io_bytes) / k["launches"],
+               "traffic_source": "ncu capture at decode step 128 scaled by keys read", "peak_source": pk["source"],
+               "launches": k["launches"], "avg_launch_ms": k["avg_ms"], "algorithmic_bytes_per_launch": (kv_bytes + io_bytes) / k["launches"]}
+        if top == "dgpt_decode_attn_partial":
+            out["note"] = ("each launch shares the GPU with the prompt-phase tensor-core kernel running on a second stream, "
+                           "so its duration is longer than alone (python bench.py --kernel-case decode_attn times it alone)")
+        return out
     if top == "dgpt_fmha_prefill":
         # shared-prompt phase per launch: QK^T and PV over rows x 1024 prompt keys, all heads: 4 * rows * P * C flops
         decode_flops = steps * L * 4 * rows * PROMPT_TOKENS * C

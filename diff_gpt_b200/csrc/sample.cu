@@ -258,6 +258,21 @@ sample_kernel(const T* __restrict__ logits, long long stride, int V, float cap, 
   }
 }
 
+// cap * tanh(x / cap) with the reference's rounding points (each op materialised in the storage type).
+template <typename T>
+__device__ __forceinline__ float softcap_value(float x, float cap) {
+  return Io<T>::round(cap * Io<T>::round(tanhf(Io<T>::round(x / cap))));
+}
+// bf16 keeps 8 bits of tanh, so the short form 1 - 2 / (e^{2|t|} + 1) (absolute error about 2e-7) gives
+// the same rounded value except within 2e-7 of a rounding boundary.
+template <>
+__device__ __forceinline__ float softcap_value<__nv_bfloat16>(float x, float cap) {
+  using B = Io<__nv_bfloat16>;
+  const float t = B::round(__fdividef(x, cap));
+  const float th = 1.f - __fdividef(2.f, __expf(2.f * fabsf(t)) + 1.f);  // e^{2|t|} = inf gives 1
+  return B::round(cap * B::round(copysignf(th, t)));
+}
+
 // ---- one warp per row -----------------------------------------------------------------------------
 // Same rule and same draw as sample_kernel, but a row is handled by one warp with shuffles only (no
 // block barriers), four rows per CTA.  exp(z - max) of the row lives in shared memory; token i sits at
@@ -289,11 +304,37 @@ sample_warp_kernel(const T* __restrict__ logits, long long stride, int R, int V,
     auto at = [&](int i) -> float& { return e[i + (i >> log2c)]; };
     const T* row = logits + (long long)r * stride;
     ArgMax best{-INFINITY, 0x7fffffff};
-    for (int i = lane; i < V; i += 32) {
-      float x = Io<T>::ld(row + i);
-      if (cap > 0.f) x = Io<T>::round(cap * Io<T>::round(tanhf(Io<T>::round(x / cap))));
-      at(i) = x;
-      if (x > best.v) best = ArgMax{x, i};
+    constexpr int VEC = Io<T>::kVec16;
+    const bool vec_ok = V % VEC == 0 && stride % VEC == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
+    if (vec_ok) {
+      // 16-byte loads, four in flight per lane; a lane visits its tokens in increasing order, so `>`
+      // keeps the lowest index among equal values, and `better` does the same across lanes
+      const int n_vec = V / VEC;
+      for (int j0 = lane; j0 < n_vec; j0 += 128) {
+        float x[4][VEC];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + 32 * u < n_vec) ld16<T>(row + (j0 + 32 * u) * VEC, x[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (j0 + 32 * u >= n_vec) continue;
+          const int i0 = (j0 + 32 * u) * VEC;
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) {
+            float v = x[u][k];
+            if (cap > 0.f) v = softcap_value<T>(v, cap);
+            at(i0 + k) = v;
+            if (v > best.v) best = ArgMax{v, i0 + k};
+          }
+        }
+      }
+    } else {
+      for (int i = lane; i < V; i += 32) {
+        float x = Io<T>::ld(row + i);
+        if (cap > 0.f) x = softcap_value<T>(x, cap);
+        at(i) = x;
+        if (x > best.v) best = ArgMax{x, i};
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -305,13 +346,22 @@ sample_warp_kernel(const T* __restrict__ logits, long long stride, int R, int V,
     token = best.i;
     if (temperature != 0.f) {
       const float zmax = best.v;
-      float part = 0.f;
-      for (int i = lane; i < V; i += 32) {
+      float p4[4] = {0.f, 0.f, 0.f, 0.f};  // four running sums: consecutive adds do not wait on one another
+      int i = lane;
+      for (; i + 96 < V; i += 128) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float ev = __expf(at(i + 32 * u) - zmax);
+          at(i + 32 * u) = ev;
+          p4[u] += ev;
+        }
+      }
+      for (; i < V; i += 32) {
         const float ev = __expf(at(i) - zmax);
         at(i) = ev;
-        part += ev;
+        p4[0] += ev;
       }
-      const float Z = warp_sum(part);
+      const float Z = warp_sum((p4[0] + p4[1]) + (p4[2] + p4[3]));
       const bool filt = top_p < 1.f;
       uint32_t key_b = 0u;
       int i_cut = V;
@@ -369,14 +419,24 @@ sample_warp_kernel(const T* __restrict__ logits, long long stride, int R, int V,
           }
           const float ek = at(pick);
           const uint32_t kk = __float_as_uint(ek);
-          float above = 0.f, before = 0.f;
-          for (int i = lane; i < V; i += 32) {
+          float a4[4] = {0.f, 0.f, 0.f, 0.f}, before = 0.f;
+          int i = lane;
+          for (; i + 96 < V; i += 128) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const float ev = at(i + 32 * u);
+              const uint32_t k = __float_as_uint(ev);
+              a4[u] += k > kk ? ev : 0.f;
+              before += (k == kk && i + 32 * u < pick) ? 1.f : 0.f;
+            }
+          }
+          for (; i < V; i += 32) {
             const float ev = at(i);
             const uint32_t k = __float_as_uint(ev);
-            above += k > kk ? ev : 0.f;
+            a4[0] += k > kk ? ev : 0.f;
             before += (k == kk && i < pick) ? 1.f : 0.f;
           }
-          above = warp_sum(above);
+          float above = warp_sum((a4[0] + a4[1]) + (a4[2] + a4[3]));
           before = warp_sum(before);
           if (above + before * ek < target) {
             token = pick;

@@ -324,14 +324,16 @@ def test_nucleus_ties_keep_lowest_ids():
 
 
 @pytest.mark.parametrize("top_p", [1.0, 0.7])
-def test_sample_inverse_cdf_with_host_philox(top_p):
+@pytest.mark.parametrize("V,dtype", [(300, torch.float32), (1024, torch.float32), (4096, torch.bfloat16), (1000, torch.bfloat16)])
+def test_sample_inverse_cdf_with_host_philox(top_p, V, dtype):
+    """V = 300 and 1000 take the scalar loads, 1024 and 4096 the 16-byte loads of the warp-per-row kernel."""
     ops = _ops()
-    R, V, seed, step0 = 64, 300, 0x1234_5678_9ABC, 5
-    logits = torch.randn(R, V, generator=torch.Generator().manual_seed(4)) * 2
+    R, seed, step0 = 64, 0x1234_5678_9ABC, 5
+    logits = (torch.randn(R, V, generator=torch.Generator().manual_seed(4)) * 2).to(dtype).float()
     out = torch.empty(R, dtype=torch.int32, device="cuda")
     step = torch.tensor([step0], dtype=torch.int32, device="cuda")
     T = 0.8
-    ops.sample(logits.cuda(), out, temperature=T, top_p=top_p, seed=seed, traj_id0=1000, step=step)
+    ops.sample(logits.to(dtype).cuda(), out, temperature=T, top_p=top_p, seed=seed, traj_id0=1000, step=step)
     got = out.cpu().tolist()
     # The kernel draws from softmax(l / T) over all tokens (attempt a uses Philox counter word 3 = a) and
     # accepts the first draw that lies in the nucleus; accepted draws follow the restricted distribution.
@@ -367,6 +369,15 @@ def test_sample_argmax_cap_force_and_history():
     assert out.cpu().tolist() == torch.argmax(15 * torch.tanh(logits / 15), -1).tolist()
     assert masks.cpu().tolist() == [1] * R and hist[:, 1].cpu().tolist() == out.cpu().tolist()
     assert hist[:, 0].cpu().tolist() == [-7] * R
+    # bf16 rows wide enough for the 16-byte loads: the soft cap is rounded to bf16 after every operation, as in
+    # the reference; the chosen token must carry the maximal capped value (ties are common at 8 bits)
+    xb = (torch.randn(5, 1024, generator=torch.Generator().manual_seed(9)) * 30).bfloat16()
+    ob = torch.empty(5, dtype=torch.int32, device="cuda")
+    ops.sample(xb.cuda(), ob, cap=15.0, temperature=0.0)
+    th = torch.tanh((xb.float() / 15).bfloat16().float()).bfloat16()
+    zb = (15 * th.float()).bfloat16().float()
+    picked = zb[torch.arange(5), ob.cpu().long()]
+    assert torch.equal(picked, zb.max(-1).values)
     # two groups of rows with their own schedule; step 1 forces group 0 only
     force = torch.tensor([[-1, 42, -1, -1], [-1, -1, 3, -1]], dtype=torch.int32, device="cuda")
     ops.sample(
