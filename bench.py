@@ -415,7 +415,8 @@ def prefill_attention(world: int, rank: int, dev, lengths=(4096, 8192, 16384, 32
             if timed:
                 ev[1].record()
             ops.fmha_prefill(q_rot, lay, y, B=B, H=H, Tq=S, D=D, q_batch_stride=S * C, q_row_stride=C,
-                             o_batch_stride=S * C, o_row_stride=C, kv_len_all=S, causal=True, impl=2, status=status)
+                             o_batch_stride=S * C, o_row_stride=C, kv_len_all=S, causal=True,
+                             impl=3 if S < 8192 else 2, status=status)  # the library's own choice, made explicit so that it cannot fall back
             if timed:
                 ev[2].record()
             torch.mm(y, wp.t(), out=proj)
@@ -553,7 +554,7 @@ def kernel_case(name: str, iters: int = 8) -> None:
 
         def launch():
             ops.fmha_prefill(q, lay, o, B=1, H=H, Tq=R, D=D, q_batch_stride=R * C, q_row_stride=C,
-                             o_batch_stride=R * C, o_row_stride=C, kv_len=klen, causal=False, lse=lse, impl=2, status=st)
+                             o_batch_stride=R * C, o_row_stride=C, kv_len=klen, causal=False, lse=lse, impl=3, status=st)
 
         work = 4 * R * P * C
         unit, peak = "TFLOP/s", pk["bf16_tflops"]

@@ -46,6 +46,20 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def _flags_changed() -> bool:
+    """True (and the record is rewritten) when the objects on disk were built with other flags."""
+    record = os.path.join(CSRC, ".build_flags")
+    now = " ".join(FLAGS)
+    try:
+        same = open(record).read() == now
+    except OSError:
+        same = False
+    if not same:
+        with open(record, "w") as f:
+            f.write(now)
+    return not same
+
+
 def _compile(src: str, verbose: bool) -> str:
     obj = src[:-3] + ".o"
     if _stale(obj, [src] + _headers() + [os.path.abspath(__file__)]):
@@ -63,6 +77,7 @@ def _compile(src: str, verbose: bool) -> str:
 def build(force: bool = False, verbose: bool = False) -> str:
     """Build (if stale) and return the path of libdgpt_b200.so."""
     srcs = _sources()
+    force = force or _flags_changed()
     if force:
         for s in srcs:
             o = s[:-3] + ".o"

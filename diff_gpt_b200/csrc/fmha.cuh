@@ -16,6 +16,7 @@ struct FmhaArgs {
   float* lse;
   int B, H, Tq, D, q_offset, causal, dtype;
   int* status;
+  int two_cta;  // tensor-core path only: the 128-thread kernel with two CTAs per SM instead of the warp-specialised one
 };
 
 // warp-level kernel (fmha_simt.cu)

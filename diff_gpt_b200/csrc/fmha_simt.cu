@@ -189,7 +189,8 @@ extern "C" int dgpt_fmha_prefill(const void* q, int64_t q_batch_stride, int64_t 
   DGPT_REQUIRE(kv_len || kv_len_all >= 0, "fmha_prefill: kv length missing");
   DGPT_REQUIRE(q_row_stride % 8 == 0 && q_batch_stride % 8 == 0 && o_row_stride % 8 == 0 && o_batch_stride % 8 == 0,
                "fmha_prefill: strides must be multiples of 8 elements");
-  DGPT_REQUIRE(impl >= 0 && impl <= 2, "fmha_prefill: impl must be 0 (auto), 1 (warp-level) or 2 (tensor-core)");
+  DGPT_REQUIRE(impl >= 0 && impl <= 3,
+               "fmha_prefill: impl must be 0 (auto), 1 (warp-level), 2 (tensor-core) or 3 (tensor-core, two CTAs per SM)");
   if (int e = validate_kv(kv, D)) return e;
   if (B == 0 || Tq == 0) return DGPT_OK;
   FmhaArgs a;
@@ -201,7 +202,12 @@ extern "C" int dgpt_fmha_prefill(const void* q, int64_t q_batch_stride, int64_t 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const KvView view = make_view(kv);
   const bool tc_ok = fmha_tc_supported(a, *kv);
-  if (impl == 2 && !tc_ok) {
+  // Which tensor-core kernel: the warp-specialised one pays off on long key ranges (measured: ahead from 8192
+  // keys on); below that, and beside the HBM-bound per-row kernel in decode, two smaller CTAs per SM do better.
+  const long long span = causal ? (long long)Tq + q_offset
+                                : (kv_len ? (long long)kv->max_pages * kv->page_tokens : (long long)kv_len_all);
+  a.two_cta = impl == 3 || (impl == 0 && span < 8192);
+  if (impl >= 2 && !tc_ok) {
     set_error("fmha_prefill: the tensor-core kernel does not cover dtype %d, head_dim %d with this layout", dtype, D);
     return DGPT_E_UNSUPPORTED;
   }

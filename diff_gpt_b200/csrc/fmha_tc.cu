@@ -16,7 +16,7 @@
 // P V done x2 (frees the P buffer and the V slot).  The K-free barriers are separate from S-ready so that
 // the loader can never run two phases ahead of a barrier it waits on.
 //
-// fmha_tc_kernel (built with -DDGPT_TC_NO_WS, kept as the simpler reference point): 128 threads, no
+// fmha_tc_kernel (impl = 3 of dgpt_fmha_prefill; the earlier, simpler form): 128 threads, no
 // fixed roles, 256 TMEM columns and two CTAs per SM so that one CTA's softmax overlaps the other's MMAs.
 //
 // No cluster launch and no multicast.  Every wait on an mbarrier is bounded in clock cycles; if one runs
@@ -949,8 +949,7 @@ int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
   size_t smem = (size_t)3 * (D / 64) * kBN * 128 + 64 + 1024;
   if (smem < 80 * 1024) smem = 80 * 1024;
   cudaError_t e;
-#ifndef DGPT_TC_NO_WS
-  {
+  if (!a.two_cta) {
     // warp-specialised kernel: Q + two K + two V tiles, padded so that one CTA owns an SM (it allocates all 512 TMEM columns)
     size_t ws_smem = (size_t)6 * (D / 64) * kBN * 128 + 256 + 1024;
     if (ws_smem < 120 * 1024) ws_smem = 120 * 1024;
@@ -967,7 +966,6 @@ int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
     }
     return launch_status("fmha_tc_ws");
   }
-#endif
   if (D == 64) {
     e = cudaFuncSetAttribute(fmha_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess) fmha_tc_kernel<64><<<grid, 128, smem, st>>>(mq, mk, mv, p);

@@ -57,25 +57,32 @@ def _run(D, B, H, Tq, Tk, pt, causal, q_offset, use_table, o_f32, impl=2, seed=0
         assert (lse[b : b + 1].cpu() - want_lse).abs().max().item() <= 2e-2
 
 
+IMPLS = [2, 3]  # 2 = warp-specialised kernel, 3 = two CTAs per SM
+
+
+@pytest.mark.parametrize("impl", IMPLS)
 @pytest.mark.parametrize("D", [64, 128])
-def test_single_tile(D):
-    _run(D, B=1, H=1, Tq=128, Tk=[128], pt=128, causal=False, q_offset=0, use_table=False, o_f32=False)
+def test_single_tile(D, impl):
+    _run(D, B=1, H=1, Tq=128, Tk=[128], pt=128, causal=False, q_offset=0, use_table=False, o_f32=False, impl=impl)
 
 
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("causal", [False, True])
-def test_multi_tile_dense(D, causal):
+@pytest.mark.parametrize("impl", IMPLS)
+def test_multi_tile_dense(D, causal, impl):
     _run(D, B=2, H=2, Tq=300, Tk=[384, 300] if not causal else [300, 300], pt=384, causal=causal, q_offset=0,
-         use_table=False, o_f32=False)
+         use_table=False, o_f32=False, impl=impl)
 
 
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("pt", [16, 64, 128])
-def test_paged_ragged_offset(D, pt):
-    _run(D, B=2, H=3, Tq=37, Tk=[48, 43], pt=pt, causal=True, q_offset=11, use_table=True, o_f32=False)
-    _run(D, B=2, H=2, Tq=200, Tk=[700, 513], pt=pt, causal=False, q_offset=0, use_table=True, o_f32=True)
+@pytest.mark.parametrize("impl", IMPLS)
+def test_paged_ragged_offset(D, pt, impl):
+    _run(D, B=2, H=3, Tq=37, Tk=[48, 43], pt=pt, causal=True, q_offset=11, use_table=True, o_f32=False, impl=impl)
+    _run(D, B=2, H=2, Tq=200, Tk=[700, 513], pt=pt, causal=False, q_offset=0, use_table=True, o_f32=True, impl=impl)
 
 
-def test_matches_warp_level_kernel_on_a_long_causal_case():
-    _run(128, B=1, H=2, Tq=1024, Tk=[1024], pt=1024, causal=True, q_offset=0, use_table=False, o_f32=False)
-    _run(64, B=1, H=2, Tq=640, Tk=[1024], pt=64, causal=True, q_offset=384, use_table=True, o_f32=False)
+@pytest.mark.parametrize("impl", IMPLS + [0])
+def test_matches_warp_level_kernel_on_a_long_causal_case(impl):
+    _run(128, B=1, H=2, Tq=1024, Tk=[1024], pt=1024, causal=True, q_offset=0, use_table=False, o_f32=False, impl=impl)
+    _run(64, B=1, H=2, Tq=640, Tk=[1024], pt=64, causal=True, q_offset=384, use_table=True, o_f32=False, impl=impl)
