@@ -491,7 +491,8 @@ def kernel_case(name: str, iters: int = 8) -> None:
 
     decode_attn: config-4 shapes at decode step 128 — 4096 trajectories x 12 heads, head_dim 64, 128 own
                  tokens per trajectory in 64-token pages, prompt partial merged, gate applied.
-    fmha:        config-5 shapes at S = 4096 — batch 8, 16 heads, head_dim 128, causal, dense K/V.
+    fmha:        config-5 shapes at S = 4096 — batch 8, 16 heads, head_dim 128, causal, dense K/V (two CTAs per SM).
+    fmha_long:   the same at S = 8192 on the warp-specialised kernel.
     sample:      config-4 logits, 4096 rows x 4096 tokens, nucleus 0.9.
     depthmix:    config-4 rows, 8 candidates (mid-stack).
     fmha_prefix: shared-prompt phase of a config-4 decode step (4096 rows x 1024 prompt keys, 12 heads x 64).
@@ -523,8 +524,11 @@ def kernel_case(name: str, iters: int = 8) -> None:
 
         work = R * (2 * C * 2 * own + 3 * C * 2 + C * 4 + H * 4)
         unit, peak = "GB/s", pk["hbm_gbs"]
-    elif name == "fmha":
-        B, H, S, D = 8, 16, 4096, 128
+    elif name in ("fmha", "fmha_long"):
+        # config-5 shapes; "fmha" = S 4096 on the two-CTAs-per-SM kernel, "fmha_long" = S 8192 on the warp-specialised
+        # one (the kernels dgpt_fmha_prefill picks by itself at those lengths)
+        B, H, S, D = 8, 16, (4096 if name == "fmha" else 8192), 128
+        which = 3 if name == "fmha" else 2
         q = torch.randn((B, S, H, D), device=dev, dtype=torch.bfloat16, generator=g)
         kv = torch.randn((B, 2, H, S, D), device=dev, dtype=torch.bfloat16, generator=g)
         lay = ops.kv_layout(kv[0, 0], kv[0, 1], 2 * H * S * D, S * D, S)
@@ -533,7 +537,7 @@ def kernel_case(name: str, iters: int = 8) -> None:
 
         def launch():
             ops.fmha_prefill(q, lay, o, B=B, H=H, Tq=S, D=D, q_batch_stride=S * H * D, q_row_stride=H * D,
-                             o_batch_stride=S * H * D, o_row_stride=H * D, kv_len_all=S, causal=True, impl=2, status=st)
+                             o_batch_stride=S * H * D, o_row_stride=H * D, kv_len_all=S, causal=True, impl=which, status=st)
 
         work = 2 * B * H * S * S * D
         unit, peak = "TFLOP/s", pk["bf16_tflops"]
@@ -609,7 +613,7 @@ def kernel_case(name: str, iters: int = 8) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel-case", default=None, choices=["decode_attn", "fmha", "sample", "depthmix", "fmha_prefix"],
+    ap.add_argument("--kernel-case", default=None, choices=["decode_attn", "fmha", "fmha_long", "sample", "depthmix", "fmha_prefix"],
                     help="run one kernel alone on a small case (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
