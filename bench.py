@@ -215,8 +215,9 @@ def run_ours(args) -> None:
     from diff_gpt_b200.dist import gather_trajectories
     from diff_gpt_b200.model.engine import DecodeRun
 
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-        os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner off stdout: rank 0 prints exactly one JSON line
+    # NCCL writes its version banner (and any debug text) to stdout unless told otherwise; rank 0 must print
+    # exactly one JSON line there, so NCCL's text goes to stderr.
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

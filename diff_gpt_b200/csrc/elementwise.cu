@@ -304,7 +304,7 @@ __global__ void swiglu_kernel<__nv_bfloat16>(const __nv_bfloat16* __restrict__ i
     for (int k = 0; k < 4; ++k) {
       const float g = fminf(x[2 * k], limit);
       const float lin = fminf(fmaxf(x[2 * k + 1], -limit), limit);
-      const float sg = B::round(1.f / (1.f + __expf(-B::round(alpha * g))));
+      const float sg = B::round(__fdividef(1.f, 1.f + __expf(-B::round(alpha * g))));
       r[k] = __float2bfloat16_rn(B::round(g * sg) * B::round(lin + 1.f));
     }
     *reinterpret_cast<uint2*>(out + i4) = *reinterpret_cast<uint2*>(r);
@@ -312,7 +312,7 @@ __global__ void swiglu_kernel<__nv_bfloat16>(const __nv_bfloat16* __restrict__ i
     for (long long i = i4; i < n_pairs; ++i) {
       const float g = fminf(B::ld(in + 2 * i), limit);
       const float lin = fminf(fmaxf(B::ld(in + 2 * i + 1), -limit), limit);
-      const float sg = B::round(1.f / (1.f + __expf(-B::round(alpha * g))));
+      const float sg = B::round(__fdividef(1.f, 1.f + __expf(-B::round(alpha * g))));
       B::st(out + i, B::round(g * sg) * B::round(lin + 1.f));
     }
   }

@@ -164,6 +164,45 @@ class DiffGPT:
         tokens = np.asarray(results[0], dtype=np.int64).reshape(-1, n_features)
         return pd.DataFrame(self._decode(start, scale, tokens), columns=names)
 
+    # ---- anomaly scores --------------------------------------------------------------------
+    @torch.inference_mode()
+    def anomaly_scores(self, df: pd.DataFrame) -> pd.DataFrame:
+        """-log p(token_t | tokens before t) per (time, channel), NaN where nothing can be scored
+        (the first max-order rows and the very first token); diff_gpt.py:295-363.
+
+        One prefill forward of the encoded signal; the negative log-likelihood of each next token is
+        taken from the logits on the device (`dgpt_token_nll`) without building the log-probability table.
+        """
+        from . import ops
+
+        columns, T = df.shape[1], df.shape[0]
+        max_order = self._max_order(columns, "columns")
+        assert max_order <= T, f"max order {max_order} > signal length {T}"
+        inp = df.to_numpy(dtype=np.float64)
+        _, _, encoded = self._encode(inp)
+        N = encoded.size
+        assert N <= self.model.block_size, (
+            f"signal has {N} tokens but block_size is {self.model.block_size}; "
+            f"chunk the input manually for longer sequences"
+        )
+        device = torch.device(self.model.device_type)
+        flat_tokens = encoded.reshape(-1).astype(np.int64)
+        tokens = torch.as_tensor(flat_tokens, dtype=torch.int64, device=device).unsqueeze(0)  # (1, N)
+        was_training = self.model.training
+        self.model.eval()
+        logits, _ = self.model.forward(tokens)  # (1, N, V); row i predicts token i + 1
+        if was_training:
+            self.model.train()
+        flat = np.full(N, np.nan, dtype=np.float64)
+        if N > 1:
+            status = torch.zeros(1, dtype=torch.int32, device=device)
+            nll = ops.token_nll(logits[0, :-1], tokens[0, 1:].to(torch.int32).contiguous(), status)
+            flat[1:] = nll.cpu().numpy().astype(np.float64)
+            assert int(status.item()) == 0, "a token id was outside the vocabulary"
+        out = np.full((T, columns), np.nan, dtype=np.float64)
+        out[max_order:] = flat.reshape(encoded.shape[0], columns)
+        return pd.DataFrame(out, columns=df.columns, index=df.index)
+
     # ---- checkpoints --------------------------------------------------------------------
     def save(self, path: str = "diff-gpt.bin") -> None:
         torch.save(self.model.state_dict(), path)

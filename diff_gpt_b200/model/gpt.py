@@ -104,6 +104,10 @@ class Block(nn.Module):
         self.mlp_res_proj = nn.Linear(n_embd, 1, bias=False)
 
 
+FUSED_FFN = True  # first feed-forward GEMM on the library's tcgen05 kernel with the SwiGLU fused (bf16 only)
+FUSED_FFN_MIN_ROWS = 256
+
+
 # ---- how one forward call is bound to K/V storage ----------------------------------
 @dataclass
 class KvBinding:
@@ -156,12 +160,15 @@ class ForwardPlan:
         self.x, self.u, self.q, self.y = buf(n, C), buf(n, C), buf(n, C), buf(n, C)
         self.qkvg = buf(n, 4 * C)
         self.parts = [buf(n, C) for _ in range(L)]
-        self.f, self.act = buf(n, 4 * C), buf(n, 2 * C)
+        self.act = buf(n, 2 * C)
         n_out = n_seq if last_only else n
         self.xn = buf(n_out, C)
         self.last = buf(n_out, C) if (last_only and T > 1) else None
         self.logits = buf(n_out, V) if want_logits else None
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        # tcgen05 GEMM + SwiGLU epilogue: bf16 with tileable sizes, and enough rows to fill the tensor cores
+        self.fused_ffn = FUSED_FFN and dt == torch.bfloat16 and C % 8 == 0 and n >= FUSED_FFN_MIN_ROWS
+        self.f = None if self.fused_ffn else buf(n, 4 * C)
         self.prefix_o = None
         self.prefix_lse = None
         self.part_o = None
@@ -255,9 +262,12 @@ class ForwardPlan:
                     torch.addmm(partial, self.y, lw.wproj_t, out=part)
             partial = part
             ops.depthmix(cands + [partial], lw.w_mlp, None, self.u)
-            with region("gemm_ffn1"):
-                torch.mm(self.u, lw.w1_t, out=self.f)
-            ops.swiglu(self.f, self.act, m.swiglu_alpha, m.swiglu_limit)
+            if self.fused_ffn:  # first FFN GEMM with the SwiGLU in its epilogue (the [n, 4C] product never reaches HBM)
+                ops.linear(self.u, lw.w1, self.act, swiglu=(m.swiglu_alpha, m.swiglu_limit), status=self.status)
+            else:
+                with region("gemm_ffn1"):
+                    torch.mm(self.u, lw.w1_t, out=self.f)
+                ops.swiglu(self.f, self.act, m.swiglu_alpha, m.swiglu_limit)
             with region("gemm_ffn2"):
                 partial.addmm_(self.act, lw.w2_t)
         final = partial
@@ -274,6 +284,7 @@ class ForwardPlan:
 
 @dataclass
 class _LayerWeights:
+    w1: torch.Tensor
     wqkvg_t: torch.Tensor
     wproj_t: torch.Tensor
     w1_t: torch.Tensor
@@ -348,6 +359,7 @@ class GPT(BaseGPT):
                 wqkvg = torch.cat([a.c_q.weight, a.c_k.weight, a.c_v.weight, a.c_g.weight], dim=0).contiguous()
                 layers.append(
                     _LayerWeights(
+                        w1=blk.ffwd.net[0].weight.detach(),
                         wqkvg_t=wqkvg.t(),
                         wproj_t=a.c_proj.weight.detach().t(),
                         w1_t=blk.ffwd.net[0].weight.detach().t(),

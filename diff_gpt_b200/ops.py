@@ -229,6 +229,46 @@ def attn_merge(
     )
 
 
+def linear(
+    a: torch.Tensor,
+    w: torch.Tensor,
+    out: torch.Tensor,
+    *,
+    swiglu: tuple[float, float] | None = None,
+    status: torch.Tensor | None = None,
+) -> None:
+    """out = a @ w.T on the tcgen05 kernel (bf16); with swiglu=(alpha, limit) the SwiGLU of interleaved column
+    pairs is applied in the epilogue and `out` has half as many columns as `w` has rows."""
+    _cuda(a, w, out, status)
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    assert out.shape == (M, N // 2 if swiglu else N) and a.dtype == w.dtype == out.dtype
+    alpha, limit = swiglu if swiglu else (0.0, 0.0)
+    check(
+        lib.dgpt_linear(
+            a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K,
+            1 if swiglu else 0, alpha, limit, dtype_code(a), _ptr(status), _stream(),
+        )
+    )
+
+
+def token_nll(logits: torch.Tensor, targets: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor:
+    """-log softmax(logits)[r, targets[r]] per row as fp32 [R]; logits [R, V] (last dim contiguous), targets int32 [R]."""
+    _cuda(logits, targets, status)
+    assert logits.dim() == 2 and logits.stride(1) == 1 and targets.dtype == torch.int32 and targets.is_contiguous()
+    R, V = logits.shape
+    assert targets.numel() == R
+    out = torch.empty(R, dtype=torch.float32, device=logits.device)
+    check(
+        lib.dgpt_token_nll(
+            logits.data_ptr(), logits.stride(0), targets.data_ptr(), out.data_ptr(), R, V, dtype_code(logits),
+            _ptr(status), _stream(),
+        )
+    )
+    return out
+
+
 def decode_attn_static_capacity_bytes() -> int:
     return int(lib.dgpt_decode_attn_static_capacity_bytes())
 

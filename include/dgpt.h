@@ -193,6 +193,27 @@ int dgpt_sigmoid_gate(void* y, int64_t y_row_stride, const void* gate, int64_t g
  * Replaces src/diff_gpt/model/gpt.py:182-186.  logits: device [n] */
 int dgpt_softcap(void* logits, int64_t n, float cap, int32_t dtype, void* stream);
 
+/* Linear layer on the tcgen05 tensor cores, optionally with the SwiGLU of the feed-forward block in its epilogue:
+ *   acc[m, n] = sum_k a[m, k] * w[n, k]                     (w as nn.Linear stores it: [N, K])
+ *   epilogue 0:  out[m, n]     = acc[m, n]                  out: [M, N]
+ *   epilogue 1:  out[m, n / 2] = swiglu(acc[m, n], acc[m, n + 1]) for even n, the rule of dgpt_swiglu applied to
+ *                the accumulator rounded to bf16 (as the reference's Linear output is)      out: [M, N / 2]
+ * Replaces nn.Linear of src/diff_gpt/model/feed_forward.py:10-14 followed by swi_glu.py:11-19 (epilogue 1), or any
+ * bias-free nn.Linear of the path (epilogue 0).  bf16 only; pointers 16-byte aligned, K and the row strides
+ * multiples of 8 elements, N a multiple of 16.  status: device int32, set non-zero if a bounded wait ran out. */
+int dgpt_linear(const void* a, int64_t a_row_stride, const void* w, int64_t w_row_stride, void* out,
+                int64_t out_row_stride, int32_t M, int32_t N, int32_t K, int32_t epilogue, float alpha,
+                float limit, int32_t dtype, int32_t* status, void* stream);
+
+/* out[r] = log(sum_j exp(logits[r, j])) - logits[r, targets[r]]: the negative log-likelihood of one given
+ * token per row, without materialising the log-probabilities.  The log-probability is rounded once to
+ * `dtype` as the reference's log_softmax output is.  Replaces the log_softmax + gather of
+ * src/diff_gpt/diff_gpt.py:352-356 (DiffGPT.anomaly_scores).
+ * logits: device [R, V] with row stride; targets: device int32 [R]; out: device fp32 [R].
+ * A target outside [0, V) gives NaN for its row and sets bit 2 of *status (status may be NULL). */
+int dgpt_token_nll(const void* logits, int64_t logits_row_stride, const int32_t* targets, float* out,
+                   int32_t R, int32_t V, int32_t dtype, int32_t* status, void* stream);
+
 /* *step_ptr += delta, as a one-thread kernel on `stream`: the last node of a captured decode step,
  * so that replaying the same launch sequence walks through the positions.  (The reference keeps the
  * position on the host: src/diff_gpt/model/kv_cache.py:113-115.) */

@@ -98,3 +98,11 @@ def mc_decode(
         if g + 1 < G:
             logits = forward(shape, w, nxt[:, None], kv=kv, table=table)[:, -1, :]
     return tokens, masks, (torch.stack(kept) if kept is not None else None)
+
+
+def token_nll(shape: Shape, w: dict, tokens: torch.Tensor) -> torch.Tensor:
+    """-log p(token_t | tokens before t) for t = 1..N-1 from one forward of the N tokens
+    (src/diff_gpt/diff_gpt.py:347-356): log_softmax of the soft-capped logits, gathered at the next token."""
+    logits = forward(shape, w, tokens.view(1, -1))[0]
+    logp = torch.log_softmax(logits[:-1], dim=-1)
+    return -logp.gather(-1, tokens.view(-1)[1:].unsqueeze(-1)).squeeze(-1)

@@ -264,6 +264,37 @@ def teacher_forced(ref):
     )
 
 
+def anomaly(ref):
+    """DiffGPT.anomaly_scores on a three-channel signal (orders [0, 1, 2]) with a tiny fp32 model, per-column and scalar order."""
+    from diff_gpt.diff_gpt import DiffGPT
+    from diff_gpt.encoder_decoder import get_domain_of_definition
+    from diff_gpt.model.gpt import GPT
+    import pandas as pd
+
+    V, C, H, L, block = 64, 32, 4, 2, 96
+    m = GPT(vocab_size=V, n_embd=C, block_size=block, n_head=H, n_layer=L).eval()
+    _init(m, 12, 0.3)
+    rng = np.random.default_rng(34)
+    x = _series(rng, 30, 3)
+    order = np.array([0, 1, 2])
+    dom = get_domain_of_definition(x, order, use_decimal=False)
+    df = pd.DataFrame(x, columns=["a", "b", "c"])
+    weights = _weights(m)
+    dg = DiffGPT(model=m, order_of_derivative=order, domain_of_definition=dom, use_decimal=False)
+    s32 = dg.anomaly_scores(df).to_numpy()
+    dg1 = DiffGPT(model=m, order_of_derivative=1, domain_of_definition=get_domain_of_definition(x, 1, use_decimal=False), use_decimal=False)
+    s32_k1 = dg1.anomaly_scores(df).to_numpy()
+    dom1 = np.asarray(dg1.domain_of_definition, dtype=np.float64)
+    # (a bf16 module cannot be scored by the reference: its .numpy() call rejects bfloat16)
+    np.savez_compressed(
+        os.path.join(HERE, "anomaly.npz"),
+        meta=np.array([V, C, H, L, block], dtype=np.int64),
+        x=x, order=order, dom=np.asarray(dom, dtype=np.float64), dom_k1=dom1,
+        scores_fp32=s32, scores_fp32_k1=s32_k1,
+        **weights,
+    )
+
+
 def main():
     ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     sys.path.insert(0, os.path.join(ref, "src"))
@@ -281,6 +312,7 @@ def main():
     engine_force(ref)
     codec(ref)
     teacher_forced(ref)
+    anomaly(ref)
 
 
 if __name__ == "__main__":

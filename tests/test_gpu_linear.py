@@ -1,0 +1,82 @@
+"""dgpt_linear (tcgen05 GEMM with the SwiGLU epilogue) against an exact matmul of the same bf16 operands."""
+
+import pytest
+import torch
+
+from oracle import ref_math
+
+pytestmark = pytest.mark.gpu
+
+
+def _operands(M, N, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    return a, w
+
+
+@pytest.mark.parametrize(
+    "M,N,K",
+    [(128, 256, 64), (4096, 3072, 768), (300, 272, 200), (1, 16, 8), (129, 528, 1000), (2048, 768, 1536)],
+)
+def test_plain_store(M, N, K):
+    """Full tiles, ragged edges in every dimension (zero-filled by TMA), one row, more tiles than SMs."""
+    from diff_gpt_b200 import ops
+
+    a, w = _operands(M, N, K, M + N + K)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.linear(a.cuda(), w.cuda(), out, status=status)
+    want = a.double() @ w.double().T
+    assert status.item() == 0
+    assert torch.isfinite(out).all()
+    err = (out.cpu().double() - want).abs().max().item()
+    assert err <= 6e-3 * want.abs().max().item(), (err, want.abs().max().item())
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (4096, 3072, 768), (77, 96, 136)])
+def test_swiglu_epilogue_equals_gemm_then_swiglu(M, N, K):
+    """Epilogue 1 = the library's own SwiGLU kernel applied to epilogue 0's output, bit for bit; and the oracle's
+    SwiGLU of the exact product within bf16 rounding."""
+    from diff_gpt_b200 import ops
+
+    a, w = _operands(M, N, K, 7 * M + K)
+    w = w * 8  # reach the clamp at 7 in a few places
+    plain = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    ops.linear(a.cuda(), w.cuda(), plain)
+    two_step = torch.empty((M, N // 2), dtype=torch.bfloat16, device="cuda")
+    ops.swiglu(plain, two_step, 1.702, 7.0)
+    fused = torch.full((M, N // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.linear(a.cuda(), w.cuda(), fused, swiglu=(1.702, 7.0))
+    assert torch.equal(fused, two_step)
+    want = ref_math.swiglu((a.double() @ w.double().T).bfloat16(), 1.702, 7.0).float()
+    err = (fused.cpu().float() - want).abs().max().item()
+    assert err <= 3e-2 * want.abs().max().item()
+
+
+def test_strided_operands_and_back_to_back_launches():
+    """Row slices of wider buffers (as the fused QKVG buffer is used) and repeated launches on one stream."""
+    from diff_gpt_b200 import ops
+
+    g = torch.Generator().manual_seed(3)
+    big_a = torch.randn(500, 4 * 128, generator=g).bfloat16().cuda()
+    w = (torch.randn(256, 128, generator=g) * 0.1).bfloat16().cuda()
+    big_out = torch.zeros(500, 3 * 256, dtype=torch.bfloat16, device="cuda")
+    a = big_a[:, 128:256]
+    for _ in range(3):
+        ops.linear(a, w, big_out[:, 256:512])
+    want = a.double().cpu() @ w.double().cpu().T
+    assert (big_out[:, 256:512].cpu().double() - want).abs().max().item() <= 6e-3 * want.abs().max().item()
+    assert big_out[:, :256].abs().max().item() == 0 and big_out[:, 512:].abs().max().item() == 0
+
+
+def test_rejects_what_it_cannot_tile():
+    from diff_gpt_b200 import ops
+    from diff_gpt_b200._lib import DgptError
+
+    a = torch.zeros(8, 12, dtype=torch.bfloat16, device="cuda")  # K = 12 is not a multiple of 8
+    w = torch.zeros(16, 12, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(DgptError):
+        ops.linear(a, w, torch.zeros(8, 16, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(DgptError):  # fp32 is not built
+        ops.linear(a.float()[:, :8].contiguous(), w.float()[:, :8].contiguous(), torch.zeros(8, 16, device="cuda"))

@@ -392,6 +392,56 @@ def test_diffgpt_facade_config1_and_teacher_forced():
     assert np.array_equal(ps, t["samples"])
 
 
+def test_anomaly_scores_match_reference_and_bf16_runs():
+    """DiffGPT.anomaly_scores (one prefill + dgpt_token_nll) against the reference's frames, NaN pattern included;
+    a bf16 module (which the reference cannot score) stays close to the fp32 scores."""
+    import pandas as pd
+
+    from diff_gpt_b200.diff_gpt import DiffGPT
+
+    g = load_golden("anomaly")
+    w = golden_weights(g, torch.float32)
+    m = _model(g["meta"], w, torch.float32)
+    df = pd.DataFrame(g["x"], columns=["a", "b", "c"], index=np.arange(100, 100 + len(g["x"])))
+    for order, dom, key in ((g["order"], g["dom"], "scores_fp32"), (1, g["dom_k1"], "scores_fp32_k1")):
+        got = DiffGPT(model=m, order_of_derivative=order, domain_of_definition=dom, use_decimal=False).anomaly_scores(df)
+        assert list(got.columns) == ["a", "b", "c"] and got.index.equals(df.index)
+        want = g[key]
+        assert np.array_equal(np.isnan(got.to_numpy()), np.isnan(want))
+        assert np.nanmax(np.abs(got.to_numpy() - want)) <= 1e-4 * np.nanmax(np.abs(want))
+    mb = _model(g["meta"], w, torch.bfloat16)
+    sb = DiffGPT(model=mb, order_of_derivative=g["order"], domain_of_definition=g["dom"], use_decimal=False).anomaly_scores(df)
+    assert np.array_equal(np.isnan(sb.to_numpy()), np.isnan(g["scores_fp32"]))
+    assert np.nanmax(np.abs(sb.to_numpy() - g["scores_fp32"])) <= 0.15  # bf16 logits of |z| <= 15 carry ~0.06 of rounding
+    with pytest.raises(AssertionError, match="block_size"):
+        big = pd.DataFrame(np.tile(g["x"], (2, 1)), columns=["a", "b", "c"])  # 58 x 3 tokens > block 96
+        DiffGPT(model=m, order_of_derivative=g["order"], domain_of_definition=g["dom"], use_decimal=False).anomaly_scores(big)
+
+
+def test_token_nll_kernel_against_torch():
+    from diff_gpt_b200 import ops
+
+    gen = torch.Generator().manual_seed(11)
+    for dtype, tol in ((torch.float32, 2e-6), (torch.bfloat16, 8e-3)):
+        for V in (7, 64, 1000, 4096):
+            x = (torch.randn(37, V, generator=gen) * 4).to(dtype)
+            t = torch.randint(0, V, (37,), generator=gen)
+            status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            got = ops.token_nll(x.cuda(), t.to(torch.int32).cuda(), status).cpu()
+            want = -torch.log_softmax(x.float(), -1).gather(-1, t[:, None])[:, 0]
+            assert (got - want).abs().max().item() <= tol * max(1.0, want.abs().max().item()), (dtype, V)
+            assert status.item() == 0
+    # a row slice with a stride, and a target outside the vocabulary: NaN for that row and a status bit
+    x = torch.randn(5, 3, 32, generator=gen).cuda()
+    t = torch.tensor([1, 2, 40, 0, 31], dtype=torch.int32).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = ops.token_nll(x[:, 1], t, status).cpu()
+    want = -torch.log_softmax(x[:, 1].cpu(), -1)
+    assert torch.isnan(got[2]) and status.item() == 4
+    for r in (0, 1, 3, 4):
+        assert abs(got[r].item() - want[r, int(t[r])].item()) <= 1e-5
+
+
 def test_kv_cache_reference_surface():
     """Lazy allocation, growth in multiples of 1024, pos on the last layer only, batch broadcast, reset
     (reference tests/diff_gpt/model/test_kv_cache.py)."""

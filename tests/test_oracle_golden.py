@@ -108,3 +108,21 @@ def test_engine_force_schedule():
     P = len(prompt)
     assert np.array_equal(toks.numpy(), g["results"][:, P:])
     assert np.array_equal(masks.numpy(), g["masks"][:, P:])
+
+
+def test_anomaly_scores_restatement():
+    """Token negative log-likelihoods of the oracle against DiffGPT.anomaly_scores of the reference."""
+    from diff_gpt_b200.encoder_decoder import encode
+
+    g = load_golden("anomaly")
+    shape = _shape(g["meta"])
+    w = golden_weights(g, torch.float32)
+    for order, dom, key in ((g["order"], g["dom"], "scores_fp32"), (1, g["dom_k1"], "scores_fp32_k1")):
+        _, _, tok = encode(inp=g["x"], vocab_size=shape.vocab_size, domain_of_definition=dom, order_of_derivative=order,
+                           use_decimal=False)
+        nll = ref_decode.token_nll(shape, w, torch.from_numpy(tok.reshape(-1).astype(np.int64))).numpy()
+        want = g[key]
+        k = int(np.max(order))
+        flat = want[k:].reshape(-1)
+        assert np.isnan(want[:k]).all() and np.isnan(flat[0]) and not np.isnan(flat[1:]).any()
+        assert np.abs(nll - flat[1:]).max() <= 1e-4
