@@ -22,6 +22,28 @@ int launch_status(const char* what);  // cudaGetLastError -> DGPT_OK / DGPT_E_CU
     }                               \
   } while (0)
 
+// ---- programmatic dependent launch ----------------------------------------------
+// A kernel launched through launch_dep may be made resident while the previous kernel on its stream is
+// still draining (that hides most of the launch latency between two dependent kernels); it must call
+// dep_wait() before it touches anything the previous kernel wrote.  dep_wait() is a no-op otherwise.
+bool dep_launch_enabled();
+__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... P, typename... A>
+inline void launch_dep(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = dep_launch_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);  // errors surface through launch_status()
+}
+
 constexpr float kRmsEps = 1.1920928955078125e-07f;  // FLT_EPSILON: F.rms_norm's default eps
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;

@@ -52,6 +52,7 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
                    float* __restrict__ part_lse, int n_splits, int R, int H, float scale_log2) {
   using Cfg = DecodeCfg<T, D>;
   constexpr int VEC = Cfg::VEC, LPT = Cfg::LPT, TPW = Cfg::TPW;
+  dep_wait();
   const long long rh = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (rh >= (long long)R * H) return;
   const int r = (int)(rh / H), h = (int)(rh - (long long)r * H);
@@ -239,6 +240,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ oa, const float* __r
                                   const T* __restrict__ gate, long long gate_stride, T* __restrict__ y,
                                   long long y_stride, int R, int H, int D) {
   constexpr int VEC = Io<T>::kVec16;
+  dep_wait();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long RH = (long long)R * H;
   const int DV = D / VEC;
@@ -289,10 +291,9 @@ static int decode_launch(const void* q, long long q_stride, const KvView& kv, co
   float* ws_o = ws ? ws + 2 * RH * n_splits : nullptr;
   const float scale_log2 = kLog2e / sqrtf((float)D);
   dim3 grid((unsigned)((RH + 3) / 4), (unsigned)n_splits);
-  decode_attn_kernel<T, D><<<grid, 128, 0, st>>>(static_cast<const T*>(q), q_stride, kv, len0, start1, len1, step_ptr,
-                                                 prefix_o, prefix_lse, static_cast<const T*>(gate), gate_stride,
-                                                 static_cast<T*>(y), y_stride, ws_ml, ws_o, part_o, part_lse, n_splits,
-                                                 R, H, scale_log2);
+  launch_dep(decode_attn_kernel<T, D>, grid, dim3(128), 0, st, static_cast<const T*>(q), q_stride, kv, len0, start1, len1,
+             step_ptr, prefix_o, prefix_lse, static_cast<const T*>(gate), gate_stride, static_cast<T*>(y), y_stride, ws_ml,
+             ws_o, part_o, part_lse, n_splits, R, H, scale_log2);
   if (int e = launch_status("decode_attn")) return e;
   if (n_splits > 1) {
     const long long n = RH * D;
@@ -412,12 +413,12 @@ extern "C" int dgpt_attn_merge(const float* o_a, const float* lse_a, const float
   const long long n = (long long)R * H * (D / (dtype == DGPT_F32 ? 4 : 8));
   const unsigned blocks = (unsigned)((n + 255) / 256);
   if (dtype == DGPT_F32) {
-    attn_merge_kernel<float><<<blocks, 256, 0, st>>>(o_a, lse_a, o_b, lse_b, static_cast<const float*>(gate),
-                                                     gate_row_stride, static_cast<float*>(y), y_row_stride, R, H, D);
+    launch_dep(attn_merge_kernel<float>, dim3(blocks), dim3(256), 0, st, o_a, lse_a, o_b, lse_b,
+               static_cast<const float*>(gate), gate_row_stride, static_cast<float*>(y), y_row_stride, R, H, D);
   } else if (dtype == DGPT_BF16) {
-    attn_merge_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(o_a, lse_a, o_b, lse_b,
-                                                             static_cast<const __nv_bfloat16*>(gate), gate_row_stride,
-                                                             static_cast<__nv_bfloat16*>(y), y_row_stride, R, H, D);
+    launch_dep(attn_merge_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, st, o_a, lse_a, o_b, lse_b,
+               static_cast<const __nv_bfloat16*>(gate), gate_row_stride, static_cast<__nv_bfloat16*>(y), y_row_stride,
+               R, H, D);
   } else {
     set_error("attn_merge: dtype %d is not built", dtype);
     return DGPT_E_UNSUPPORTED;

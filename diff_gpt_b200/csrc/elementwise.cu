@@ -26,6 +26,13 @@ int launch_status(const char* what) {
   return DGPT_OK;
 }
 
+// Dependent launches are on unless DGPT_DEP_LAUNCH=0 is in the environment (read at every launch, so a test
+// can compare both forms in one process).
+bool dep_launch_enabled() {
+  const char* e = getenv("DGPT_DEP_LAUNCH");
+  return !(e && e[0] == '0');
+}
+
 // ---- embedding gather + RMSNorm ---------------------------------------------
 // One warp per token.  The row is read twice (second read hits L1/L2).
 template <typename T>
@@ -134,6 +141,7 @@ depthmix_vec_kernel(CandPtrs cands, int n_cands, const T* __restrict__ w, T* __r
                     T* __restrict__ out_rn, long long rows, int C) {
   constexpr int VEC = Io<T>::kVec16;
   constexpr int E = NV * VEC;
+  dep_wait();
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -244,9 +252,9 @@ static int depthmix_launch(const CandPtrs& cp, int n, const void* w, void* out_h
   const unsigned grid = (unsigned)((rows + warps - 1) / warps);
   if (depthmix_vec_ok<T>(cp, n, w, out_h, out_rn, C)) {
     const int nv = (C / Io<T>::kVec16 + 31) / 32;
-#define DGPT_MIXV(N)                                                                           \
-  depthmix_vec_kernel<T, N><<<grid, warps * 32, 0, st>>>(cp, n, static_cast<const T*>(w),      \
-                                                         static_cast<T*>(out_h), static_cast<T*>(out_rn), rows, C)
+#define DGPT_MIXV(N)                                                                              \
+  launch_dep(depthmix_vec_kernel<T, N>, dim3(grid), dim3(warps * 32), 0, st, cp, n, static_cast<const T*>(w), \
+             static_cast<T*>(out_h), static_cast<T*>(out_rn), rows, C)
     if (nv <= 1) DGPT_MIXV(1);
     else if (nv <= 2) DGPT_MIXV(2);
     else if (nv <= 3) DGPT_MIXV(3);

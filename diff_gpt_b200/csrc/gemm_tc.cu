@@ -77,6 +77,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  dep_wait();  // everything above touched only this CTA's own shared memory and TMEM
 
   if (warp == 9) {
     // ================= loader =================
@@ -265,6 +266,6 @@ extern "C" int dgpt_linear(const void* a, int64_t a_row_stride, const void* w, i
   }
   const int tiles = ((M + tc::kGM - 1) / tc::kGM) * ((N + tc::kGN - 1) / tc::kGN);
   const int grid = tiles < n_sm[dev] ? tiles : n_sm[dev];
-  tc::gemm_tc_kernel<<<grid, tc::kGThreads, smem, st>>>(ma, mw, p);
+  launch_dep(tc::gemm_tc_kernel, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
   return launch_status("linear");
 }

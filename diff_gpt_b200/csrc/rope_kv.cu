@@ -109,6 +109,7 @@ __global__ void rope_qknorm_kvappend_vec_kernel(const T* __restrict__ q, const T
   constexpr int VEC = Io<T>::kVec16;
   constexpr int LPH = D / VEC;
   static_assert(LPH >= 1 && LPH <= 32 && (LPH & (LPH - 1)) == 0, "unsupported head_dim");
+  dep_wait();
   const long long unit = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LPH;  // (token, head)
   const int e = threadIdx.x % LPH;
   const long long total = (long long)n_seq * T_len * H;
@@ -162,9 +163,9 @@ static int rope_vec_launch(const void* q, const void* k, const void* v, long lon
   constexpr int LPH = D / Io<T>::kVec16;
   const long long threads = (long long)n_seq * T_len * H * LPH;
   const unsigned grid = (unsigned)((threads + 255) / 256);
-  rope_qknorm_kvappend_vec_kernel<T, D><<<grid, 256, 0, st>>>(
-      static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(v), in_stride, static_cast<T*>(q_out),
-      q_out_stride, static_cast<const T*>(cs), table_len, view, pos0, slot0, step_ptr, n_seq, T_len, H, status);
+  launch_dep(rope_qknorm_kvappend_vec_kernel<T, D>, dim3(grid), dim3(256), 0, st, static_cast<const T*>(q),
+             static_cast<const T*>(k), static_cast<const T*>(v), in_stride, static_cast<T*>(q_out), q_out_stride,
+             static_cast<const T*>(cs), table_len, view, pos0, slot0, step_ptr, n_seq, T_len, H, status);
   return launch_status("rope_qknorm_kvappend");
 }
 

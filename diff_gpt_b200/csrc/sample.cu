@@ -290,6 +290,7 @@ sample_warp_kernel(const T* __restrict__ logits, long long stride, int R, int V,
                    int* __restrict__ out_mask, int* __restrict__ hist_tok, int* __restrict__ hist_mask,
                    long long hist_stride) {
   extern __shared__ __align__(16) float smem[];
+  dep_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int r = blockIdx.x * kWarpRows + warp;
   if (r >= R) return;
@@ -597,10 +598,9 @@ static int sample_launch(const void* logits, long long stride, int R, int V, flo
         return DGPT_E_CUDA;
       }
     }
-    wk<<<(R + kWarpRows - 1) / kWarpRows, 32 * kWarpRows, wsmem, st>>>(
-        static_cast<const T*>(logits), stride, R, V, log2c, cap, temperature, top_p, (uint32_t)seed,
-        (uint32_t)(seed >> 32), traj_id0, traj_ids, step_base, step_ptr, force, force_rows, force_stride, out_tok,
-        out_mask, hist_tok, hist_mask, hist_stride);
+    launch_dep(wk, dim3((R + kWarpRows - 1) / kWarpRows), dim3(32 * kWarpRows), wsmem, st, static_cast<const T*>(logits),
+               stride, R, V, log2c, cap, temperature, top_p, (uint32_t)seed, (uint32_t)(seed >> 32), traj_id0, traj_ids,
+               step_base, step_ptr, force, force_rows, force_stride, out_tok, out_mask, hist_tok, hist_mask, hist_stride);
     return launch_status("sample");
   }
   const size_t smem = (size_t)V * 2 * sizeof(float);

@@ -106,6 +106,7 @@ class Block(nn.Module):
 
 FUSED_FFN = True  # first feed-forward GEMM on the library's tcgen05 kernel with the SwiGLU fused (bf16 only)
 FUSED_FFN_MIN_ROWS = 256
+SIDE_PRIORITY = -1  # stream of the shared-prompt attention phase: ahead of the per-row phase it runs beside
 
 
 # ---- how one forward call is bound to K/V storage ----------------------------------
@@ -186,7 +187,7 @@ class ForwardPlan:
         if b.shared_layouts is not None and b.overlap_prefix and b.n_splits == 1 and self.part_o is None:
             self.part_o = torch.empty((self.n, H, D), dtype=torch.float32, device=dev)
             self.part_lse = torch.empty((self.n, H), dtype=torch.float32, device=dev)
-            self.side = torch.cuda.Stream(device=dev, priority=-1)
+            self.side = torch.cuda.Stream(device=dev, priority=SIDE_PRIORITY)
         if b.n_splits > 1 and self.workspace is None:
             nbytes = ops.decode_attn_workspace_bytes(self.n, H, D, b.n_splits)
             self.workspace = torch.empty(nbytes // 4, dtype=torch.float32, device=dev)
