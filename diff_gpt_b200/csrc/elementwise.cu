@@ -26,11 +26,12 @@ int launch_status(const char* what) {
   return DGPT_OK;
 }
 
-// Dependent launches are on unless DGPT_DEP_LAUNCH=0 is in the environment (read at every launch, so a test
-// can compare both forms in one process).
+// Dependent launches are off unless DGPT_DEP_LAUNCH=1 is in the environment (read at every launch, so both
+// forms can be compared in one process).  Measured on the config-4 decode step: 1291 ms per 255 steps with
+// them, 1272 ms without - blocks made resident early take room from the kernel that is still running.
 bool dep_launch_enabled() {
   const char* e = getenv("DGPT_DEP_LAUNCH");
-  return !(e && e[0] == '0');
+  return e && e[0] == '1';
 }
 
 // ---- embedding gather + RMSNorm ---------------------------------------------
