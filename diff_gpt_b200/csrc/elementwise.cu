@@ -60,6 +60,7 @@ __global__ void embed_rmsnorm_kernel(const int* __restrict__ ids, const T* __res
 constexpr int kMaxCands = 64;
 struct CandPtrs {
   const void* p[kMaxCands];
+  unsigned char mult[kMaxCands];  // how many times the candidate occurs in the caller's list (read once, weighted)
 };
 
 // One warp per row, one pass over the candidates with an online softmax across
@@ -103,7 +104,7 @@ __global__ void depthmix_kernel(CandPtrs cands, int n_cands, const T* __restrict
     dot = Io<T>::round(warp_sum(dot));
     const float m_new = fmaxf(m, dot);
     const float resc = __expf(m - m_new);
-    const float p = __expf(dot - m_new);
+    const float p = __expf(dot - m_new) * (float)cands.mult[n];
     l = l * resc + p;
 #pragma unroll
     for (int i = 0; i < EPL; ++i) acc[i] = acc[i] * resc + p * v[i];
@@ -213,7 +214,7 @@ depthmix_vec_kernel(CandPtrs cands, int n_cands, const T* __restrict__ w, T* __r
       for (int x = 0; x < E; ++x) acc[x] *= resc;
       m = dot;
     }
-    const float pw = __expf(dot - m);
+    const float pw = __expf(dot - m) * (float)cands.mult[n];
     l += pw;
 #pragma unroll
     for (int x = 0; x < E; ++x) acc[x] += pw * v[x];
@@ -394,11 +395,22 @@ int dgpt_depthmix(const void* const* cands, int32_t n_cands, const void* w, void
   DGPT_REQUIRE(out_h || out_rn, "depthmix: no output requested");
   DGPT_REQUIRE(rows >= 0 && C > 0, "depthmix: bad sizes");
   if (rows == 0) return DGPT_OK;
+  // A candidate listed several times (the reference commits the embedding twice) is read once and its
+  // softmax weight multiplied: p v + p v = 2 p v exactly.
   CandPtrs cp;
+  int n_unique = 0;
   for (int i = 0; i < n_cands; ++i) {
     DGPT_REQUIRE(cands[i], "depthmix: candidate %d is NULL", i);
-    cp.p[i] = cands[i];
+    int j = 0;
+    while (j < n_unique && cp.p[j] != cands[i]) ++j;
+    if (j == n_unique) {
+      cp.p[n_unique] = cands[i];
+      cp.mult[n_unique++] = 1;
+    } else {
+      ++cp.mult[j];
+    }
   }
+  n_cands = n_unique;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == DGPT_F32) return depthmix_launch<float>(cp, n_cands, w, out_h, out_rn, rows, C, st);
   if (dtype == DGPT_BF16) return depthmix_launch<__nv_bfloat16>(cp, n_cands, w, out_h, out_rn, rows, C, st);

@@ -4,10 +4,12 @@
 //   acc[m, n] = sum_k A[m, k] * W[n, k]        A: activations [M, K] bf16, W: nn.Linear weight [N, K] bf16
 //   mode 0:  out[m, n]     = bf16(acc[m, n])
 //   mode 1:  out[m, n / 2] = swiglu(bf16(acc[m, n]), bf16(acc[m, n + 1]))   for even n  (interleaved gate / linear)
+//   mode 2:  out[m, n]     = bf16(resid[m, n] + acc[m, n])                    (the residual add of addmm, one rounding)
 //
-// Persistent, warp-specialised CTAs of 320 threads, one per SM, tiles of 128 x 256 outputs taken round robin:
-//   warp 9, lane 0  loader: TMA loads of the A (128 x 64) and W (256 x 64) blocks, 128-byte swizzle, ring of 4
-//   warp 8, lane 0  issuer: four tcgen05.mma (M 128, N 256, K 16) per block into one of two TMEM accumulators
+// Persistent, warp-specialised CTAs of 320 threads, one per SM, tiles of 128 x BN outputs (BN = 256, 192 or 128,
+// whichever needs the fewest rounds of tiles over the SMs) taken round robin:
+//   warp 9, lane 0  loader: TMA loads of the A (128 x 64) and W (BN x 64) blocks, 128-byte swizzle, ring of 4
+//   warp 8, lane 0  issuer: four tcgen05.mma (M 128, N BN, K 16) per block into one of two TMEM accumulators
 //   warps 0-7       epilogue: warp w owns the 32 output rows (TMEM lanes) 32 (w % 4) .. and the column half w / 4;
 //                   it reads the finished accumulator 32 columns at a time, applies the epilogue and stores bf16
 // so the epilogue of tile i runs while the tensor cores work on tile i + 1.  No cluster, no multicast.
@@ -18,15 +20,19 @@
 namespace dgpt {
 namespace tc {
 
-constexpr int kGM = 128, kGN = 256, kGK = 64, kGStages = 4;
-constexpr uint32_t kGABytes = kGM * 128, kGBBytes = kGN * 128, kGStageBytes = kGABytes + kGBBytes;
+constexpr int kGM = 128, kGK = 64, kGStages = 4;  // the tile is 128 x BN outputs, BN = 256, 192 or 128
+constexpr uint32_t kGABytes = kGM * 128;
 constexpr int kGThreads = 320;  // 8 epilogue warps, the MMA issuer's warp, the loader's warp
 constexpr int kGEpiThreads = 256;
-constexpr uint32_t kGIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kGN >> 3) << 17) | ((uint32_t)(kGM >> 4) << 24);
+__host__ __device__ constexpr uint32_t gemm_idesc(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kGM >> 4) << 24);
+}
 
 struct GemmParams {
   __nv_bfloat16* out;
   long long out_rs;
+  const __nv_bfloat16* resid;  // mode 2: added to the accumulator before the one rounding (may alias out)
+  long long resid_rs;
   int M, N, K, mode;
   float alpha, limit;
   int* status;
@@ -39,8 +45,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+template <int BN>
 __global__ void __launch_bounds__(kGThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ CUtensorMap mw, const GemmParams p) {
+  constexpr int kGN = BN;
+  constexpr uint32_t kGBBytes = kGN * 128, kGStageBytes = kGABytes + kGBBytes;
+  constexpr uint32_t kGIdesc = gemm_idesc(BN);
+  constexpr int kAccStride = 256;  // TMEM columns between the two accumulators
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kGStages * kGStageBytes);
@@ -126,7 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
           const uint32_t sa = a0 + s * kGStageBytes, sb = sa + kGABytes;
 #pragma unroll
           for (int ks = 0; ks < kGK / 16; ++ks)
-            umma_ss(tmem + a * kGN, smem_desc(sa + ks * 32, 16, 1024), smem_desc(sb + ks * 32, 16, 1024), kGIdesc,
+            umma_ss(tmem + a * kAccStride, smem_desc(sa + ks * 32, 16, 1024), smem_desc(sb + ks * 32, 16, 1024), kGIdesc,
                     (kb > 0 || ks > 0) ? 1u : 0u);
           umma_commit(bar_empty + 8 * s);  // the slot is free once these MMAs have read it
         }
@@ -156,13 +167,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
 #pragma unroll 1
       for (int c = c_begin; c < c_begin + kGN / 2; c += 32) {
         float v[32];
-        tmem_ld32(lane_addr + a * kGN + c, v);  // all lanes load; stores below are predicated
+        tmem_ld32(lane_addr + a * kAccStride + c, v);  // all lanes load; stores below are predicated
         if (row >= p.M) continue;
-        if (p.mode == 0) {
+        if (p.mode == 0 || p.mode == 2) {
           __nv_bfloat16* dst = p.out + (long long)row * p.out_rs + col0 + c;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             if (col0 + c + 8 * q >= p.N) break;  // N is a multiple of 8
+            if (p.mode == 2) {
+              float r8[8];
+              ld16<__nv_bfloat16>(p.resid + (long long)row * p.resid_rs + col0 + c + 8 * q, r8);
+#pragma unroll
+              for (int x = 0; x < 8; ++x) v[8 * q + x] += r8[x];
+            }
             st16<__nv_bfloat16>(dst + 8 * q, v + 8 * q, 1.f);
           }
         } else {
@@ -217,18 +234,20 @@ static bool encode_2d(CUtensorMap* map, const void* base, long long rows, long l
 using namespace dgpt;
 
 extern "C" int dgpt_linear(const void* a, int64_t a_row_stride, const void* w, int64_t w_row_stride, void* out,
-                           int64_t out_row_stride, int32_t M, int32_t N, int32_t K, int32_t epilogue, float alpha,
-                           float limit, int32_t dtype, int32_t* status, void* stream) {
+                           int64_t out_row_stride, const void* resid, int64_t resid_row_stride, int32_t M, int32_t N,
+                           int32_t K, int32_t epilogue, float alpha, float limit, int32_t dtype, int32_t* status,
+                           void* stream) {
   DGPT_REQUIRE(a && w && out, "linear: NULL pointer");
   DGPT_REQUIRE(M >= 0 && N > 0 && K > 0, "linear: bad sizes");
-  DGPT_REQUIRE(epilogue == 0 || epilogue == 1, "linear: epilogue must be 0 (store) or 1 (SwiGLU of interleaved pairs)");
+  DGPT_REQUIRE(epilogue >= 0 && epilogue <= 2, "linear: epilogue must be 0 (store), 1 (SwiGLU of interleaved pairs) or 2 (add)");
+  DGPT_REQUIRE(epilogue != 2 || resid, "linear: epilogue 2 needs the matrix to add");
   if (dtype != DGPT_BF16) {
     set_error("linear: only bf16 is built (dtype %d)", dtype);
     return DGPT_E_UNSUPPORTED;
   }
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (!al(a) || !al(w) || !al(out) || K % 8 != 0 || N % 16 != 0 || a_row_stride % 8 != 0 || w_row_stride % 8 != 0 ||
-      out_row_stride % 8 != 0) {
+      out_row_stride % 8 != 0 || (epilogue == 2 && (!al(resid) || resid_row_stride % 8 != 0))) {
     set_error("linear: pointers must be 16-byte aligned, K and the row strides multiples of 8, N a multiple of 16");
     return DGPT_E_UNSUPPORTED;
   }
@@ -237,35 +256,55 @@ extern "C" int dgpt_linear(const void* a, int64_t a_row_stride, const void* w, i
     set_error("linear: needs an sm_100 device and cuTensorMapEncodeTiled");
     return DGPT_E_UNSUPPORTED;
   }
-  CUtensorMap ma, mw;
-  if (!tc::encode_2d(&ma, a, M, K, a_row_stride, tc::kGM) || !tc::encode_2d(&mw, w, N, K, w_row_stride, tc::kGN))
-    return DGPT_E_CUDA;
-  tc::GemmParams p;
-  p.out = static_cast<__nv_bfloat16*>(out);
-  p.out_rs = out_row_stride;
-  p.M = M; p.N = N; p.K = K; p.mode = epilogue;
-  p.alpha = alpha; p.limit = limit;
-  p.status = status;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Tile width: the one that needs the fewest rounds of tiles over the SMs, then the widest (fewest bytes moved)
   static int n_sm[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     set_error("linear: cudaGetDevice failed");
     return DGPT_E_CUDA;
   }
-  const size_t smem = (size_t)tc::kGStages * tc::kGStageBytes + 256 + 1024;
   if (n_sm[dev] == 0) {
     int n = 0;
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    cudaError_t e = cudaFuncSetAttribute(tc::gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaSuccess;
+    const int big = (int)((size_t)tc::kGStages * (tc::kGABytes + 256 * 128) + 256 + 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::gemm_tc_kernel<192>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
     if (e != cudaSuccess || n <= 0) {
       set_error("linear: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       return DGPT_E_CUDA;
     }
     n_sm[dev] = n;
   }
-  const int tiles = ((M + tc::kGM - 1) / tc::kGM) * ((N + tc::kGN - 1) / tc::kGN);
+  const int tiles_m = (M + tc::kGM - 1) / tc::kGM;
+  int bn = 256;
+  double best = 1e30;
+  for (int cand : {256, 192, 128}) {
+    const int tiles = tiles_m * ((N + cand - 1) / cand);
+    const double cost = (double)((tiles + n_sm[dev] - 1) / n_sm[dev]) * cand;  // rounds x time of one tile
+    if (cost < best - 1e-9) {
+      best = cost;
+      bn = cand;
+    }
+  }
+  CUtensorMap ma, mw;
+  if (!tc::encode_2d(&ma, a, M, K, a_row_stride, tc::kGM) || !tc::encode_2d(&mw, w, N, K, w_row_stride, bn))
+    return DGPT_E_CUDA;
+  tc::GemmParams p;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_rs = out_row_stride;
+  p.resid = static_cast<const __nv_bfloat16*>(resid);
+  p.resid_rs = resid_row_stride;
+  p.M = M; p.N = N; p.K = K; p.mode = epilogue;
+  p.alpha = alpha; p.limit = limit;
+  p.status = status;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)tc::kGStages * (tc::kGABytes + (size_t)bn * 128) + 256 + 1024;
+  const int tiles = tiles_m * ((N + bn - 1) / bn);
   const int grid = tiles < n_sm[dev] ? tiles : n_sm[dev];
-  launch_dep(tc::gemm_tc_kernel, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
+  if (bn == 256) launch_dep(tc::gemm_tc_kernel<256>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
+  else if (bn == 192) launch_dep(tc::gemm_tc_kernel<192>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
+  else launch_dep(tc::gemm_tc_kernel<128>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
   return launch_status("linear");
 }

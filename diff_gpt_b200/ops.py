@@ -235,20 +235,26 @@ def linear(
     out: torch.Tensor,
     *,
     swiglu: tuple[float, float] | None = None,
+    add: torch.Tensor | None = None,
     status: torch.Tensor | None = None,
 ) -> None:
-    """out = a @ w.T on the tcgen05 kernel (bf16); with swiglu=(alpha, limit) the SwiGLU of interleaved column
-    pairs is applied in the epilogue and `out` has half as many columns as `w` has rows."""
-    _cuda(a, w, out, status)
+    """out = a @ w.T on the tcgen05 kernel (bf16).  swiglu=(alpha, limit): the SwiGLU of interleaved column pairs is
+    applied in the epilogue and `out` has half as many columns as `w` has rows.  add=r: out = r + a @ w.T, rounded
+    once (r may be `out`)."""
+    _cuda(a, w, out, add, status)
+    assert not (swiglu and add is not None)
     M, K = a.shape
     N = w.shape[0]
     assert w.shape[1] == K and a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
     assert out.shape == (M, N // 2 if swiglu else N) and a.dtype == w.dtype == out.dtype
+    if add is not None:
+        assert add.shape == out.shape and add.dtype == out.dtype and add.stride(1) == 1
     alpha, limit = swiglu if swiglu else (0.0, 0.0)
     check(
         lib.dgpt_linear(
-            a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K,
-            1 if swiglu else 0, alpha, limit, dtype_code(a), _ptr(status), _stream(),
+            a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), _ptr(add),
+            0 if add is None else add.stride(0), M, N, K, 1 if swiglu else (2 if add is not None else 0), alpha, limit,
+            dtype_code(a), _ptr(status), _stream(),
         )
     )
 

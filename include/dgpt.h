@@ -198,12 +198,15 @@ int dgpt_softcap(void* logits, int64_t n, float cap, int32_t dtype, void* stream
  *   epilogue 0:  out[m, n]     = acc[m, n]                  out: [M, N]
  *   epilogue 1:  out[m, n / 2] = swiglu(acc[m, n], acc[m, n + 1]) for even n, the rule of dgpt_swiglu applied to
  *                the accumulator rounded to bf16 (as the reference's Linear output is)      out: [M, N / 2]
- * Replaces nn.Linear of src/diff_gpt/model/feed_forward.py:10-14 followed by swi_glu.py:11-19 (epilogue 1), or any
- * bias-free nn.Linear of the path (epilogue 0).  bf16 only; pointers 16-byte aligned, K and the row strides
+ *   epilogue 2:  out[m, n]     = resid[m, n] + acc[m, n], rounded once (resid may be out itself)   out: [M, N]
+ * Replaces nn.Linear of src/diff_gpt/model/feed_forward.py:10-14 followed by swi_glu.py:11-19 (epilogue 1), any
+ * bias-free nn.Linear of the path (epilogue 0), or a projection with the residual add that follows it
+ * (src/diff_gpt/model/block.py:98-106, epilogue 2).  resid is ignored for epilogues 0 and 1.  bf16 only; pointers 16-byte aligned, K and the row strides
  * multiples of 8 elements, N a multiple of 16.  status: device int32, set non-zero if a bounded wait ran out. */
 int dgpt_linear(const void* a, int64_t a_row_stride, const void* w, int64_t w_row_stride, void* out,
-                int64_t out_row_stride, int32_t M, int32_t N, int32_t K, int32_t epilogue, float alpha,
-                float limit, int32_t dtype, int32_t* status, void* stream);
+                int64_t out_row_stride, const void* resid, int64_t resid_row_stride, int32_t M, int32_t N,
+                int32_t K, int32_t epilogue, float alpha, float limit, int32_t dtype, int32_t* status,
+                void* stream);
 
 /* out[r] = log(sum_j exp(logits[r, j])) - logits[r, targets[r]]: the negative log-likelihood of one given
  * token per row, without materialising the log-probabilities.  The log-probability is rounded once to

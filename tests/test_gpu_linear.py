@@ -80,3 +80,26 @@ def test_rejects_what_it_cannot_tile():
         ops.linear(a, w, torch.zeros(8, 16, dtype=torch.bfloat16, device="cuda"))
     with pytest.raises(DgptError):  # fp32 is not built
         ops.linear(a.float()[:, :8].contiguous(), w.float()[:, :8].contiguous(), torch.zeros(8, 16, device="cuda"))
+
+
+@pytest.mark.parametrize("M,N,K", [(4096, 768, 768), (4096, 768, 1536), (300, 400, 136), (2048, 128, 64)])
+def test_add_epilogue_in_place_and_narrow_tiles(M, N, K):
+    """out = resid + a @ w.T with one rounding, in place and into another buffer; N = 768 / 400 / 128 pick the
+    192- and 128-wide tiles."""
+    from diff_gpt_b200 import ops
+
+    a, w = _operands(M, N, K, 3 * M + N)
+    g = torch.Generator().manual_seed(5)
+    resid = torch.randn(M, N, generator=g).bfloat16()
+    want = (resid.double() + a.double() @ w.double().T)
+    other = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    r_dev = resid.cuda()
+    ops.linear(a.cuda(), w.cuda(), other, add=r_dev)
+    assert torch.equal(r_dev.cpu(), resid)  # the addend is only read
+    in_place = resid.cuda()
+    ops.linear(a.cuda(), w.cuda(), in_place, add=in_place)
+    assert torch.equal(in_place, other)
+    err = (other.cpu().double() - want).abs().max().item()
+    assert err <= 6e-3 * want.abs().max().item()
+    ref = torch.addmm(resid.cuda(), a.cuda(), w.cuda().t())  # cuBLAS: same single rounding, other summation order
+    assert (other.float() - ref.float()).abs().max().item() <= 2e-2 * want.abs().max().item()

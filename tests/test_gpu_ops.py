@@ -63,6 +63,16 @@ def test_depthmix_golden_and_random(dtype, tol, tag):
         out = torch.empty(9, C, dtype=dtype, device="cuda")
         ops.depthmix([t.cuda() for t in cs], wv.cuda(), out, None)
         assert _rel(out, want) <= (2e-5 if dtype == torch.float32 else 3e-2), C
+    # the same device buffer listed twice (read once, weight doubled) against two separate copies of it;
+    # and a list that is one buffer repeated: the mix is that buffer
+    base = [(torch.randn(10, 768, generator=gen) * (1 + i)).to(dtype).cuda() for i in range(4)]
+    wv = (torch.randn(768, generator=gen) * 0.2).to(dtype).cuda()
+    o_same, o_copy, o_one = (torch.empty(10, 768, dtype=dtype, device="cuda") for _ in range(3))
+    ops.depthmix([base[0], base[0], base[1], base[2], base[0], base[3]], wv, o_same, None)
+    ops.depthmix([base[0], base[0].clone(), base[1], base[2], base[0].clone(), base[3]], wv, o_copy, None)
+    assert _rel(o_same, o_copy) <= (1e-6 if dtype == torch.float32 else 8e-3)
+    ops.depthmix([base[1], base[1], base[1]], wv, o_one, None)
+    assert torch.equal(o_one, base[1])
     # candidate counts on both sides of the shared-memory-staged kernel's limit (32), odd row count
     for n_c in (2, 3, 13, 17, 32, 33):
         cs = [(torch.randn(11, 768, generator=gen) * (1 + 0.3 * i)).to(dtype) for i in range(n_c)]
