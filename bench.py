@@ -41,6 +41,23 @@ PROMPT_TOKENS, HORIZON, TRAJECTORIES, N_SERIES = 1024, 256, 4096, 32
 TOP_P, TEMPERATURE, WEIGHT_SEED = 0.9, 1.0, 4
 
 
+_RESULT_OUT = None
+
+
+def claim_stdout() -> None:
+    """Keep stdout for the one JSON line: libraries that print there (NCCL's version banner) are sent to stderr."""
+    global _RESULT_OUT
+    if _RESULT_OUT is None:
+        sys.stdout.flush()
+        _RESULT_OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    out = _RESULT_OUT if _RESULT_OUT is not None else sys.stdout
+    print(json.dumps(line), file=out, flush=True)
+
+
 def peaks() -> dict:
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -185,14 +202,14 @@ def run_reference(args) -> None:
         n += cpu_step(shape, w, prompt)
     dt = time.perf_counter() - t0
     v = n / dt
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": "mc_decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args.gpus),
         "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": cpu_sample_text()},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }), flush=True)
+    })
 
 
 def workload_config(n_gpus: int) -> dict:
@@ -215,9 +232,6 @@ def run_ours(args) -> None:
     from diff_gpt_b200.dist import gather_trajectories
     from diff_gpt_b200.model.engine import DecodeRun
 
-    # NCCL writes its version banner (and any debug text) to stdout unless told otherwise; rank 0 must print
-    # exactly one JSON line there, so NCCL's text goes to stderr.
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -376,7 +390,7 @@ def run_ours(args) -> None:
             },
             "prefill_attention": prefill, "kernels": kernels, "status_ok": status_ok,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -635,6 +649,7 @@ def main() -> None:
     if args.kernel_case:
         kernel_case(args.kernel_case)
         return
+    claim_stdout()
     if args.impl == "reference":
         run_reference(args)
     else:
