@@ -85,3 +85,74 @@ def test_config5_shape_attention_layer_bf16_head_dim_128(S):
     out = torch.mm(y, wp.cuda().t()).view(B, S, C).float().cpu()
     assert status.item() == 0
     assert (out - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+
+
+# ---- full BASELINE sizes, checked through properties that do not need the CPU oracle -------------------
+def test_config4_full_size_shards_reproduce_the_whole_and_argmax_rows_agree():
+    """One series of config 4 at full size (12 layers, 12 heads of 64, 1024-token prompt, 4096 trajectories,
+    horizon 32 to keep the test short): (a) decoding trajectories [0, 2048) and [2048, 4096) separately gives
+    exactly the tokens of the whole run (the random stream is keyed by trajectory id, and no kernel's result
+    may depend on which rows share a launch); (b) under argmax all 4096 rows produce one and the same stream;
+    (c) forced steps are honoured in every row; (d) nucleus draws stay inside the nucleus of their row."""
+    import bench
+    from diff_gpt_b200 import GPT, Engine, NucleusSampler, TemperatureSampler
+
+    w = bench.cfg4_weights(torch.bfloat16)
+    m = GPT(**bench.CFG4).eval()
+    sd = dict(w)
+    sd["lm_head.weight"] = sd["token_embedding_table.weight"]
+    m.load_state_dict(sd)
+    m = m.to(torch.bfloat16).cuda()
+    prompt = bench.synthetic_prompts(1, bench.CFG4["vocab_size"])[0]
+    assert len(prompt) == 1024
+    N, G = 4096, 32
+    s = NucleusSampler(0.9, TemperatureSampler(1.0))
+    eng = Engine(m)
+    whole, _ = eng.generate_many([prompt], N, G, s, seed=42)
+    lo, _ = eng.generate_many([prompt], N // 2, G, s, seed=42, traj_offset=0)
+    hi, _ = eng.generate_many([prompt], N // 2, G, s, seed=42, traj_offset=N // 2)
+    assert torch.equal(whole[:, : N // 2], lo) and torch.equal(whole[:, N // 2 :], hi)
+    assert int(whole.min()) >= 0 and int(whole.max()) < bench.CFG4["vocab_size"]
+    assert len({tuple(r) for r in whole[0, :64].cpu().tolist()}) > 32  # trajectories differ
+    sched = [None] * G
+    sched[3], sched[17] = 7, 4000
+    greedy, masks = eng.generate_many([prompt], N, G, TemperatureSampler(0.0), force_schedules=[sched])
+    assert bool((greedy[0] == greedy[0, :1]).all())
+    assert bool((greedy[0, :, 3] == 7).all()) and bool((greedy[0, :, 17] == 4000).all())
+    assert masks[0, 0].cpu().tolist() == [0 if i in (3, 17) else 1 for i in range(G)]
+    eng.release()
+
+
+@pytest.mark.parametrize("S", [4096, 8192])
+def test_config5_full_size_the_two_tensor_core_kernels_agree_and_attention_is_linear_in_v(S):
+    """Config 5 at full size (batch 8, 16 heads of 128, causal): the warp-specialised kernel and the
+    two-CTAs-per-SM kernel are different programs and must agree within bf16 rounding; the output is linear
+    in V (att(q, k, 2 v1 - v2) = 2 att(v1) - att(v2)); row 0 of every sequence sees one key, so it returns v[0]."""
+    from diff_gpt_b200 import ops
+
+    B, H, D = 8, 16, 128
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn((B, S, H, D), device="cuda", dtype=torch.bfloat16, generator=g)
+    k = torch.randn((B, H, S, D), device="cuda", dtype=torch.bfloat16, generator=g)
+    v1 = torch.randn((B, H, S, D), device="cuda", dtype=torch.bfloat16, generator=g)
+    v2 = torch.randn((B, H, S, D), device="cuda", dtype=torch.bfloat16, generator=g)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def att(v, impl):
+        o = torch.empty_like(q)
+        lay = ops.kv_layout(k, v, page_stride=H * S * D, head_stride=S * D, page_tokens=S)
+        ops.fmha_prefill(q, lay, o, B=B, H=H, Tq=S, D=D, q_batch_stride=S * H * D, q_row_stride=H * D,
+                         o_batch_stride=S * H * D, o_row_stride=H * D, kv_len_all=S, causal=True, impl=impl, status=status)
+        return o.float()
+
+    a2, a3 = att(v1, 2), att(v1, 3)
+    assert status.item() == 0
+    scale = a2.abs().max().item()
+    assert (a2 - a3).abs().max().item() <= 1.5e-2 * scale
+    assert torch.equal(a2[:, 0], v1[:, :, 0].float()) and torch.equal(a3[:, 0], v1[:, :, 0].float())
+    mix = (2 * v1.float() - v2.float()).bfloat16()
+    lin = 2 * a2 - att(v2, 2)
+    got = att(mix, 2)
+    assert (got - lin).abs().max().item() <= 4e-2 * lin.abs().max().item()
+    # late rows average many values: their magnitude shrinks like 1/sqrt(keys) for these random inputs
+    assert a2[:, -64:].abs().mean().item() < 0.25 * a2[:, :4].abs().mean().item()
