@@ -202,11 +202,11 @@ extern "C" int dgpt_fmha_prefill(const void* q, int64_t q_batch_stride, int64_t 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const KvView view = make_view(kv);
   const bool tc_ok = fmha_tc_supported(a, *kv);
-  // Which tensor-core kernel: the warp-specialised one pays off on long key ranges (measured: ahead from 8192
+  // Which tensor-core kernel: the warp-specialised one pays off on long key ranges (measured: ahead from 4096
   // keys on); below that, and beside the HBM-bound per-row kernel in decode, two smaller CTAs per SM do better.
   const long long span = causal ? (long long)Tq + q_offset
                                 : (kv_len ? (long long)kv->max_pages * kv->page_tokens : (long long)kv_len_all);
-  a.two_cta = impl == 3 || (impl == 0 && span < 8192);
+  a.two_cta = impl == 3 || (impl == 0 && span < 4096);
   if (impl >= 2 && !tc_ok) {
     set_error("fmha_prefill: the tensor-core kernel does not cover dtype %d, head_dim %d with this layout", dtype, D);
     return DGPT_E_UNSUPPORTED;

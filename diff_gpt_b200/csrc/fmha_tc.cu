@@ -1,20 +1,25 @@
 // tcgen05 / TMEM attention for bf16, head_dim 64 or 128 (sm_100a): causal / chunk prefill, and the
 // shared-prompt phase of the Monte-Carlo decode (all trajectories of a series against the prompt K/V).
 //
-// fmha_tc_ws_kernel (the one that runs): one CTA of 192 threads per 128-query tile of one (batch, head),
-// one CTA per SM, all 512 TMEM columns.  The warps have fixed roles:
-//   warp 5, lane 0  loader: TMA loads of Q (once) and of the K / V tiles (128-byte swizzle, one box per
+// fmha_tc_ws_kernel (impl = 2 of dgpt_fmha_prefill, chosen from 4096 keys on): one CTA of 320 threads per
+// 128-query tile of one (batch, head), one CTA per SM, all 512 TMEM columns.  The warps have fixed roles:
+//   warp 9, lane 0  loader: TMA loads of Q (once) and of the K / V tiles (128-byte swizzle, one box per
 //                   page and per 64-wide half of D) into a ring of 3 K slots and 2 V slots
-//   warp 4, lane 0  issuer: S_j = Q K_j^T into one of two S buffers in TMEM, and O += P_j V_j with P read
+//   warp 8, lane 0  issuer: S_j = Q K_j^T into one of two S buffers in TMEM, and O += P_j V_j with P read
 //                   from TMEM (A operand) and V MN-major; it issues P V for tile j, then S for tile j + 2,
 //                   so the tensor cores work on one tile while the softmax warps work on the next
-//   warps 0-3       softmax: thread t owns query row t = TMEM lane t; reads S with tcgen05.ld, keeps the
-//                   running maximum and sum, writes P as packed bf16 into one of two P buffers
-//                   (tcgen05.st) and rescales O in TMEM only when the maximum has moved by more than 2^8
+//   warps 0-7       softmax, two threads per query row: warp w owns the TMEM lanes of quarter w & 3 and the
+//                   key columns of half w >> 2.  A thread reads its 64 scores with tcgen05.ld, swaps its
+//                   partial maximum with the row's other thread through an 8-byte shared-memory word
+//                   (value + turn number, polled with the same clock limit as every wait), writes P as
+//                   packed bf16 into one of two P buffers (tcgen05.st) and rescales its half of O in TMEM
+//                   only when the maximum has moved by more than 2^8.  Two warps per scheduler keep the
+//                   exp2 unit fed while the other instructions of the tile issue (with one thread per row
+//                   a tile took about 1680 cycles of softmax against 1024 of MMA).
 // TMEM columns: S0 [0,128)  S1 [128,256)  P0 [256,320)  P1 [320,384)  O [384, 384 + D).
-// mbarriers: Q loaded; K slot full x3 / free x3; V slot full x2; S ready x2; P ready x2 (128 arrivals);
-// P V done x2 (frees the P buffer and the V slot).  The K-free barriers are separate from S-ready so that
-// the loader can never run two phases ahead of a barrier it waits on.
+// mbarriers: Q loaded; K slot full x3 / free x3; V slot full x2; S ready x2; P ready x2 (256 arrivals);
+// P V done x2 (frees the P buffer and the V slot).  The K-free barriers are separate from
+// S-ready so that the loader can never run two phases ahead of a barrier it waits on.
 //
 // fmha_tc_kernel (impl = 3 of dgpt_fmha_prefill; the earlier, simpler form): 128 threads, no
 // fixed roles, 256 TMEM columns and two CTAs per SM so that one CTA's softmax overlaps the other's MMAs.
@@ -320,12 +325,12 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
 #ifdef DGPT_TC_PROF
 __device__ long long g_prof[16];
 #define PROF_T(k) const long long prof_t##k = clock64()
-#define PROF_ADD(i, a, b) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 33 || tid == 128)) g_prof[i] += prof_t##b - prof_t##a; } while (0)
+#define PROF_ADD(i, a, b) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 33 || tid == 256)) g_prof[i] += prof_t##b - prof_t##a; } while (0)
 #else
 #define PROF_T(k)
 #define PROF_ADD(i, a, b)
 #endif
-constexpr int kWsThreads = 192;
+constexpr int kWsThreads = 320;  // 8 softmax warps, the MMA issuer's warp, the loader's warp
 constexpr uint32_t kWsTmemCols = 512;
 
 template <int D>
@@ -346,6 +351,8 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // [2 turns][2 halves][128 rows] words of (turn number + 1) << 32 | value: what the two threads of a row exchange
+  volatile unsigned long long* xch = reinterpret_cast<volatile unsigned long long*>(bars + 32);
   const uint32_t aQ = smem_u32(smem), aK = aQ + kTileBytes, aV = aQ + 4 * kTileBytes;
   const uint32_t bar_q = smem_u32(bars);
   const uint32_t bar_k0 = bar_q + 8, bar_v0 = bar_q + 32, bar_s0 = bar_q + 48, bar_p0 = bar_q + 64, bar_o0 = bar_q + 80,
@@ -369,11 +376,15 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       mbar_init(bar_k0 + 8 * i, 1);
       mbar_init(bar_v0 + 8 * i, 1);
       mbar_init(bar_s0 + 8 * i, 1);
-      mbar_init(bar_p0 + 8 * i, kBM);
+      mbar_init(bar_p0 + 8 * i, 2 * kBM);
       mbar_init(bar_o0 + 8 * i, 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
+  }
+  if (tid < 2 * kBM) {  // turn numbers of a previous CTA on this SM must not be mistaken for this one's
+    xch[tid] = 0ull;
+    xch[2 * kBM + tid] = 0ull;
   }
   if (warp == 0) {
     tmem_alloc(smem_u32(tmem_slot), kWsTmemCols);
@@ -385,7 +396,7 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   const uint32_t tmem = *tmem_slot;
   bool fail = false;
 
-  if (warp == 5) {
+  if (warp == 9) {
     // ================= loader: every TMA load (one lane) =================
     if ((tid & 31) == 0 && n_tiles > 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&mq)) : "memory");
@@ -452,7 +463,7 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           if (last_v[i] >= 0) mbar_wait(bar_v0 + 8 * i, (uint32_t)last_v[i]);
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     // ================= MMA issuer (one lane) =================
     if ((tid & 31) == 0 && n_tiles > 0) {
       constexpr int kStepsS = D / 16, kStepsPV = kBN / 16;
@@ -515,9 +526,35 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       }
     }
   } else {
-    // ================= softmax threads: one query row each =================
-    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    // ================= softmax threads: two per query row, one for each half of the key tile =================
+    // Warp w works on the TMEM lanes of quarter w & 3 (the only ones it can reach) and on columns
+    // [64 (w >> 2), +64) of S.  The two threads of a row exchange their partial maxima (and, at the end,
+    // their partial sums) through shared memory, handing over with an mbarrier per pair of warps so that
+    // the wait is bounded like every other wait here.
+    constexpr int kHalf = kBN / 2;
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + (tid & 31);
+    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     float m = -INFINITY, l = 0.f;
+    // Hand-over of one float between the two threads of a row: value and turn number travel in one 8-byte
+    // shared-memory word (a single store, so no fence is needed), slots alternate with the turn's parity,
+    // and the reader polls with a clock-cycle limit like every other wait of this kernel.
+    auto exchange = [&](float mine, int turn, bool& ok) -> float {  // returns the partner's value
+      const int xb = turn & 1;
+      const unsigned long long want = (unsigned long long)(turn + 1) << 32;
+      xch[(xb * 2 + half) * kBM + row] = want | __float_as_uint(mine);
+      const volatile unsigned long long* src = xch + (xb * 2 + (half ^ 1)) * kBM + row;
+      const long long t_begin = clock64();
+      for (int spin = 0;; ++spin) {
+        const unsigned long long got = *src;  // one 8-byte load of what one 8-byte store wrote
+        if ((got >> 32) == (unsigned long long)(turn + 1)) return __uint_as_float((uint32_t)got);
+        if ((spin & 63) == 63 && (*abort_flag || clock64() - t_begin > kWaitLimitCycles)) {
+          if (!*abort_flag) *abort_flag = 27;
+          ok = false;
+          return 0.f;
+        }
+      }
+    };
     for (int j = 0; j < n_tiles; ++j) {
       const int buf = j & 1;
       const uint32_t ph = (uint32_t)((j >> 1) & 1);
@@ -535,10 +572,10 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           fail = true;
           break;
         }
-        if (tid >= valid_rows) {  // value rows past the end may hold anything: clear them so that 0 * x stays 0
+        if (half == 0 && row >= valid_rows) {  // value rows past the end may hold anything: clear them so that 0 * x stays 0
 #pragma unroll
           for (int s = 0; s < kSub; ++s) {
-            uint4* vrow = reinterpret_cast<uint4*>(sV + buf * kTileBytes + s * kSubBytes + tid * 128);
+            uint4* vrow = reinterpret_cast<uint4*>(sV + buf * kTileBytes + s * kSubBytes + row * 128);
 #pragma unroll
             for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
           }
@@ -546,25 +583,33 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         }
       }
       const bool need_mask = (t0 + kBN > klen) || (p.causal && t0 + kBN - 1 > p.q_offset + q0);
-      const int last_key = p.causal ? min(klen - 1, p.q_offset + q0 + tid) : klen - 1;
-      float sv[kBN];
-#pragma unroll
+      const int last_key = p.causal ? min(klen - 1, p.q_offset + q0 + row) : klen - 1;
+      const int c0 = t0 + half * kHalf;  // key index of this thread's first column
+      float sv[kHalf];
       PROF_T(1);
-      for (int c = 0; c < 4; ++c) tmem_ld32_nowait(lane_addr + buf * 128 + c * 32, &sv[c * 32]);
+#pragma unroll
+      for (int c = 0; c < kHalf / 32; ++c) tmem_ld32_nowait(lane_addr + buf * 128 + half * kHalf + c * 32, &sv[c * 32]);
       tc_wait_ld();
       PROF_T(2);
       float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < kBN; ++i) {
-          sv[i] = (t0 + i <= last_key) ? sv[i] : -INFINITY;
+        for (int i = 0; i < kHalf; ++i) {
+          sv[i] = (c0 + i <= last_key) ? sv[i] : -INFINITY;
           mxs[i & 3] = fmaxf(mxs[i & 3], sv[i]);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < kBN; ++i) mxs[i & 3] = fmaxf(mxs[i & 3], sv[i]);
+        for (int i = 0; i < kHalf; ++i) mxs[i & 3] = fmaxf(mxs[i & 3], sv[i]);
       }
-      const float mx2 = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * p.scale_log2;
+      const float mine = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
+      bool xok = true;
+      const float theirs = exchange(mine, j, xok);
+      if (!__all_sync(0xffffffffu, xok)) {
+        fail = true;
+        break;
+      }
+      const float mx2 = fmaxf(mine, theirs) * p.scale_log2;  // the same number in both threads of the row
       float alpha = 1.f;  // lazy rescale: the running maximum only moves when exceeded by 2^8
       if (mx2 > m + 8.f || m == -INFINITY) {
         alpha = (m == -INFINITY) ? 0.f : ex2(m - mx2);
@@ -580,19 +625,19 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         }
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < D / 64; ++c) {  // this thread's half of the row's O columns
           float v[32];
-          tmem_ld32(lane_addr + kOCol + c * 32, v);
+          tmem_ld32(lane_addr + kOCol + half * (D / 2) + c * 32, v);
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] *= alpha;
-          tmem_st32(lane_addr + kOCol + c * 32, v);
+          tmem_st32(lane_addr + kOCol + half * (D / 2) + c * 32, v);
         }
       }
       const float m_use = (m == -INFINITY) ? 0.f : m;
       PROF_T(3);
       float rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < kHalf / 32; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -602,9 +647,9 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
           packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
         }
-        tmem_st16(lane_addr + kPCol + buf * 64 + c * 16, packed);
+        tmem_st16(lane_addr + kPCol + buf * 64 + half * (kHalf / 2) + c * 16, packed);
       }
-      l = l * alpha + ((rs[0] + rs[1]) + (rs[2] + rs[3]));
+      l = l * alpha + ((rs[0] + rs[1]) + (rs[2] + rs[3]));  // sum over this thread's columns only
       PROF_T(4);
       tc_wait_st();
       tc_fence_before();
@@ -625,16 +670,22 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       if (!wait_or_abort(bar_o0 + 8 * (last & 1), (uint32_t)((last >> 1) & 1), abort_flag, 26)) fail = true;
       tc_fence_after();
     }
+    if (!__any_sync(0xffffffffu, fail) && n_tiles > 0) {  // the row's sum is the sum of its two halves
+      bool xok = true;
+      const float theirs = exchange(l, n_tiles, xok);
+      if (xok) l += theirs;
+      else fail = true;
+    }
     if (!__any_sync(0xffffffffu, fail)) {
-      const int qi = q0 + tid;
+      const int qi = q0 + row;
       const bool row_ok = qi < p.Tq;
       const float inv = (l > 0.f && n_tiles > 0) ? 1.f / l : 0.f;
-      const long long off = (long long)b * p.o_bs + (long long)qi * p.o_rs + (long long)h * D;
+      const long long off = (long long)b * p.o_bs + (long long)qi * p.o_rs + (long long)h * D + half * (D / 2);
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         float v[32];
         if (n_tiles > 0) {
-          tmem_ld32(lane_addr + kOCol + c * 32, v);
+          tmem_ld32(lane_addr + kOCol + half * (D / 2) + c * 32, v);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0.f;
@@ -652,7 +703,8 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           }
         }
       }
-      if (row_ok && p.lse) p.lse[((long long)b * p.Tq + qi) * p.H + h] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
+      if (half == 0 && row_ok && p.lse)
+        p.lse[((long long)b * p.Tq + qi) * p.H + h] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
     } else if (p.status) {
       atomicExch(p.status, *abort_flag ? *abort_flag : 2);
     }
@@ -745,7 +797,7 @@ int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
   cudaError_t e;
   if (!a.two_cta) {
     // warp-specialised kernel: Q + two K + two V tiles, padded so that one CTA owns an SM (it allocates all 512 TMEM columns)
-    size_t ws_smem = (size_t)6 * (D / 64) * kBN * 128 + 256 + 1024;
+    size_t ws_smem = (size_t)6 * (D / 64) * kBN * 128 + 8192 + 1024;  // tiles, barriers and exchange area, alignment slack
     if (ws_smem < 120 * 1024) ws_smem = 120 * 1024;
     if (D == 64) {
       e = cudaFuncSetAttribute(fmha_tc_ws_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ws_smem);

@@ -109,7 +109,7 @@ int dgpt_rope_qknorm_kvappend(const void* q, const void* k, const void* v, int64
  * kv: sequence index = b;  kv_len: device int32 [B] or NULL (then kv_len_all is used).
  * impl: 0 = choose (bf16 with D = 64 or 128 runs on the tcgen05 tensor cores, everything else takes
  * the warp-level online-softmax kernel; of the two tensor-core kernels the warp-specialised one is taken
- * from 8192 keys on, the two-CTAs-per-SM one below), 1 = warp-level kernel, 2 = warp-specialised
+ * from 4096 keys on, the two-CTAs-per-SM one below), 1 = warp-level kernel, 2 = warp-specialised
  * tensor-core kernel or fail, 3 = tensor-core kernel with two CTAs per SM or fail.
  * status: device int32, set non-zero if a bounded wait inside the tensor-core kernel ran out. */
 int dgpt_fmha_prefill(const void* q, int64_t q_batch_stride, int64_t q_row_stride,
