@@ -19,7 +19,7 @@ import torch
 
 from .encoder_decoder import decode, encode
 from .model.engine import Engine
-from .model.gpt import BaseGPT
+from .model.gpt import GPT, BaseGPT
 from .sampler.sampler import Sampler
 
 
@@ -78,10 +78,18 @@ class DiffGPT:
         )
         start, scale, encoded = self._encode(df.to_numpy(dtype=np.float64))
         prompt = encoded.reshape(-1).astype(np.int64).tolist()  # row-major: (time, channel)
-        results, _ = Engine(model=self.model).generate_batch(
-            tokens=prompt, num_samples=num_samples, max_tokens=max_new_points * columns, sampler=sampler
-        )
-        tokens = np.asarray(results, dtype=np.int64).reshape(num_samples, -1, columns)
+        engine = Engine(model=self.model)
+        if isinstance(self.model, GPT):
+            # tokens stay in one device tensor until a single copy to the host: no per-trajectory Python lists
+            generated, _ = engine.generate_many([prompt], num_samples, max_new_points * columns, sampler)
+            generated = generated[0].cpu().numpy().astype(np.int64)  # (N, G)
+            head = np.broadcast_to(np.asarray(prompt, dtype=np.int64)[None, :], (num_samples, len(prompt)))
+            tokens = np.concatenate([head, generated], axis=1).reshape(num_samples, -1, columns)
+        else:
+            results, _ = engine.generate_batch(
+                tokens=prompt, num_samples=num_samples, max_tokens=max_new_points * columns, sampler=sampler
+            )
+            tokens = np.asarray(results, dtype=np.int64).reshape(num_samples, -1, columns)
         values = self._decode(start, scale, tokens)  # (N, rows + new, F), all trajectories at once
         return np.ascontiguousarray(values[:, rows : rows + max_new_points, :])
 
