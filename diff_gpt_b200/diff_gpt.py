@@ -23,6 +23,22 @@ from .model.gpt import GPT, BaseGPT
 from .sampler.sampler import Sampler
 
 
+def _quantile_of_sorted(ordered: torch.Tensor, q: float) -> torch.Tensor:
+    """np.quantile(x, q, axis=0) with its default linear method, on values already sorted along axis 0, with the
+    same float64 operations numpy performs (its _lerp): a + (b - a) t, and b - (b - a)(1 - t) where t >= 0.5.
+    Every product and sum is a separate rounded operation, as in numpy."""
+    n = ordered.shape[0]
+    virtual = (n - 1) * q
+    lo = int(np.floor(virtual))
+    hi = min(lo + 1, n - 1)
+    t = virtual - lo
+    a, b = ordered[lo], ordered[hi]
+    diff = b - a
+    if t >= 0.5:
+        return b - diff * (1 - t)
+    return a + diff * t
+
+
 class DiffGPT:
     __slots__ = ("model", "order_of_derivative", "domain_of_definition", "use_decimal")
 
@@ -61,8 +77,7 @@ class DiffGPT:
         )
 
     # ---- Monte-Carlo futures ---------------------------------------------------------
-    def _generate_future_samples(self, df: pd.DataFrame, max_new_points: int, sampler: Sampler | None, num_samples: int) -> np.ndarray:
-        """(num_samples, max_new_points, n_features) float64: the forecast rows only."""
+    def _check_future_request(self, df: pd.DataFrame, max_new_points: int, num_samples: int) -> None:
         assert num_samples >= 1
         rows, columns = df.shape
         max_order = self._max_order(columns, "columns")
@@ -76,20 +91,39 @@ class DiffGPT:
             f"{columns} columns (max_order={max_order}) require {total_positions} "
             f"context positions, but block_size is {self.model.block_size}"
         )
+
+    def _future_samples_on_device(self, df: pd.DataFrame, max_new_points: int, sampler: Sampler | None, num_samples: int) -> torch.Tensor:
+        """(num_samples, max_new_points, n_features) float64 ON THE DEVICE: tokens are decoded where they were
+        sampled (`dgpt_integrate_tokens`), continuing the cumulative sums from the state the context leaves."""
+        from . import ops
+        from .encoder_decoder import _orders, integrate_end_state
+
+        columns = df.shape[1]
         start, scale, encoded = self._encode(df.to_numpy(dtype=np.float64))
         prompt = encoded.reshape(-1).astype(np.int64).tolist()  # row-major: (time, channel)
-        engine = Engine(model=self.model)
+        generated, _ = Engine(model=self.model).generate_many([prompt], num_samples, max_new_points * columns, sampler)
+        V = self.model.vocab_size
+        scale_cols = np.array(np.broadcast_to(np.asarray(scale, dtype=np.float64).reshape(-1), (columns,)))  # a writable copy
+        state = integrate_end_state(start, (encoded - V // 2) / scale, self.order_of_derivative)
+        dev = generated.device
+        return ops.integrate_tokens(
+            generated[0], columns, V, torch.from_numpy(scale_cols).to(dev),
+            torch.from_numpy(_orders(self.order_of_derivative, columns).astype(np.int32)).to(dev),
+            torch.from_numpy(state).to(dev),
+        )
+
+    def _generate_future_samples(self, df: pd.DataFrame, max_new_points: int, sampler: Sampler | None, num_samples: int) -> np.ndarray:
+        """(num_samples, max_new_points, n_features) float64: the forecast rows only."""
+        self._check_future_request(df, max_new_points, num_samples)
+        rows, columns = df.shape
         if isinstance(self.model, GPT):
-            # tokens stay in one device tensor until a single copy to the host: no per-trajectory Python lists
-            generated, _ = engine.generate_many([prompt], num_samples, max_new_points * columns, sampler)
-            generated = generated[0].cpu().numpy().astype(np.int64)  # (N, G)
-            head = np.broadcast_to(np.asarray(prompt, dtype=np.int64)[None, :], (num_samples, len(prompt)))
-            tokens = np.concatenate([head, generated], axis=1).reshape(num_samples, -1, columns)
-        else:
-            results, _ = engine.generate_batch(
-                tokens=prompt, num_samples=num_samples, max_tokens=max_new_points * columns, sampler=sampler
-            )
-            tokens = np.asarray(results, dtype=np.int64).reshape(num_samples, -1, columns)
+            return self._future_samples_on_device(df, max_new_points, sampler, num_samples).cpu().numpy()
+        start, scale, encoded = self._encode(df.to_numpy(dtype=np.float64))
+        prompt = encoded.reshape(-1).astype(np.int64).tolist()  # row-major: (time, channel)
+        results, _ = Engine(model=self.model).generate_batch(
+            tokens=prompt, num_samples=num_samples, max_tokens=max_new_points * columns, sampler=sampler
+        )
+        tokens = np.asarray(results, dtype=np.int64).reshape(num_samples, -1, columns)
         values = self._decode(start, scale, tokens)  # (N, rows + new, F), all trajectories at once
         return np.ascontiguousarray(values[:, rows : rows + max_new_points, :])
 
@@ -108,6 +142,14 @@ class DiffGPT:
     ) -> dict[float, pd.DataFrame]:
         for q in quantiles:
             assert 0.0 < q < 1.0, f"quantile {q} must be in (0, 1)"
+        if isinstance(self.model, GPT):
+            self._check_future_request(df, max_new_points, num_samples)
+            futures = self._future_samples_on_device(df, max_new_points, sampler, num_samples)
+            ordered = torch.sort(futures, dim=0).values  # (N, H, F) sorted over the trajectories
+            return {
+                float(q): pd.DataFrame(_quantile_of_sorted(ordered, float(q)).cpu().numpy(), columns=df.columns)
+                for q in quantiles
+            }
         futures = self._generate_future_samples(df=df, max_new_points=max_new_points, sampler=sampler, num_samples=num_samples)
         return {float(q): pd.DataFrame(np.quantile(futures, q, axis=0), columns=df.columns) for q in quantiles}
 

@@ -120,6 +120,31 @@ def integrate(start: np.ndarray, diff: np.ndarray, order_of_derivative, use_deci
     return out
 
 
+def integrate_end_state(start: np.ndarray, diff: np.ndarray, order_of_derivative) -> np.ndarray:
+    """Running sums that `integrate` has reached after the last row of `diff` (N, F), per column and level:
+    result[c, m] = last element of the (m + 1)-th cumulative sum of column c, zeros beyond the column's order.
+    Continuing the sums from this state reproduces `integrate` over a longer sequence addition for addition."""
+    n_cols = diff.shape[-1]
+    orders = _orders(order_of_derivative, n_cols)
+    scalar = _scalar(order_of_derivative)
+    max_k = start.shape[0]
+    state = np.zeros((n_cols, max(max_k, 1)), dtype=np.float64)
+    for c, k in enumerate(orders):
+        k = int(k)
+        if scalar:
+            firsts = [start[i, c] for i in range(k)]
+        else:
+            firsts, level = [], start[max_k - k : max_k, c]
+            for _ in range(k):
+                firsts.append(level[0])
+                level = np.diff(level)
+        col = diff[:, c]
+        for i in range(k):
+            col = np.cumsum(np.concatenate([np.array([firsts[k - 1 - i]], dtype=np.float64), col]))
+            state[c, i] = col[-1]
+    return state
+
+
 def _carry_sigma_delta(x: np.ndarray, vocab_size: int) -> np.ndarray:
     """First-order scheme: integer part plus the increments of the rounded running fraction."""
     whole = np.trunc(x)

@@ -259,6 +259,26 @@ def linear(
     )
 
 
+def integrate_tokens(
+    tokens: torch.Tensor, n_chan: int, vocab_size: int, scale: torch.Tensor, order: torch.Tensor, state: torch.Tensor
+) -> torch.Tensor:
+    """(token - V/2) / scale followed by order[c] cumulative sums continued from `state`: int32 [N, H * F] -> f64 [N, H, F]."""
+    _cuda(tokens, scale, order, state)
+    assert tokens.dtype == torch.int32 and tokens.dim() == 2 and tokens.stride(1) == 1 and tokens.shape[1] % n_chan == 0
+    assert scale.dtype == torch.float64 and state.dtype == torch.float64 and order.dtype == torch.int32
+    assert scale.shape == (n_chan,) and order.shape == (n_chan,) and state.dim() == 2 and state.shape[0] == n_chan
+    assert scale.is_contiguous() and order.is_contiguous() and state.is_contiguous()
+    N, horizon = tokens.shape[0], tokens.shape[1] // n_chan
+    out = torch.empty((N, horizon, n_chan), dtype=torch.float64, device=tokens.device)
+    check(
+        lib.dgpt_integrate_tokens(
+            tokens.data_ptr(), tokens.stride(0), N, horizon, n_chan, vocab_size, scale.data_ptr(), order.data_ptr(),
+            state.data_ptr(), state.shape[1], out.data_ptr(), _stream(),
+        )
+    )
+    return out
+
+
 def token_nll(logits: torch.Tensor, targets: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor:
     """-log softmax(logits)[r, targets[r]] per row as fp32 [R]; logits [R, V] (last dim contiguous), targets int32 [R]."""
     _cuda(logits, targets, status)

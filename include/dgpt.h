@@ -217,6 +217,19 @@ int dgpt_linear(const void* a, int64_t a_row_stride, const void* w, int64_t w_ro
 int dgpt_token_nll(const void* logits, int64_t logits_row_stride, const int32_t* targets, float* out,
                    int32_t R, int32_t V, int32_t dtype, int32_t* status, void* stream);
 
+/* Generated tokens -> float64 values for all trajectories of a series at once:
+ *   value = (token - vocab_size / 2) / scale[channel], then order[channel] cumulative sums in time order,
+ *   continued from the running sums the context leaves behind (state[channel][m] = level m + 1 at the end of
+ *   the prompt).  Each addition has the operands and the order of the reference's numpy cumsum over the whole
+ *   sequence, so the results are bit-identical to decoding every trajectory on the host.
+ * Replaces the per-sample decode loop of src/diff_gpt/diff_gpt.py:236-252 (encoder_decoder.py:373-397, :97-152).
+ * tokens: device int32 [n_traj, horizon * n_chan] (time-major, channel fastest) with row stride;
+ * scale: device f64 [n_chan]; order: device int32 [n_chan] (each <= max_order <= 8);
+ * state: device f64 [n_chan, max_order]; out: device f64 [n_traj, horizon, n_chan]. */
+int dgpt_integrate_tokens(const int32_t* tokens, int64_t token_row_stride, int32_t n_traj, int32_t horizon,
+                          int32_t n_chan, int32_t vocab_size, const double* scale, const int32_t* order,
+                          const double* state, int32_t max_order, double* out, void* stream);
+
 /* *step_ptr += delta, as a one-thread kernel on `stream`: the last node of a captured decode step,
  * so that replaying the same launch sequence walks through the positions.  (The reference keeps the
  * position on the host: src/diff_gpt/model/kv_cache.py:113-115.) */

@@ -44,3 +44,41 @@ def test_decimal_mode_is_refused():
     x = np.zeros((4, 1))
     with pytest.raises(NotImplementedError):
         get_domain_of_definition(x, 1, use_decimal=True)
+
+
+def test_cumulative_sums_can_be_continued_from_their_end_state():
+    """integrate_end_state + one addition per level and step reproduces integrate over the longer sequence
+    bit for bit (what the device-side decode of the generated horizon relies on)."""
+    from diff_gpt_b200.encoder_decoder import _orders, integrate, integrate_end_state
+
+    rng = np.random.default_rng(0)
+    for order in (0, 1, 2, 3, np.array([0, 1, 2, 2, 1])):
+        F, Tp, H = 5, 17, 9
+        max_k = int(np.max(order))
+        start = rng.normal(size=(max_k, F))
+        head, tail = rng.normal(size=(Tp, F)), rng.normal(size=(H, F))
+        whole = integrate(start, np.concatenate([head, tail], 0), order)
+        state = integrate_end_state(start, head, order)
+        got = np.zeros((H, F))
+        for c, k in enumerate(_orders(order, F)):
+            x = state[c].copy()
+            for t in range(H):
+                v = tail[t, c]
+                for m in range(int(k)):
+                    x[m] = x[m] + v
+                    v = x[m]
+                got[t, c] = v
+        assert np.array_equal(got, whole[max_k + Tp :])
+
+
+def test_quantile_of_sorted_equals_numpy_linear_quantile():
+    import torch
+
+    from diff_gpt_b200.diff_gpt import _quantile_of_sorted
+
+    rng = np.random.default_rng(1)
+    for n in (1, 2, 7, 100, 4096):
+        x = rng.normal(size=(n, 6, 3)) * 1e3
+        ordered = torch.sort(torch.from_numpy(x), dim=0).values
+        for q in (0.1, 0.25, 0.5, 0.9, 0.999):
+            assert np.array_equal(_quantile_of_sorted(ordered, q).numpy(), np.quantile(x, q, axis=0)), (n, q)

@@ -465,3 +465,44 @@ def test_kv_cache_reference_surface():
     assert wide.get_pos() == 3 and torch.equal(wide.kv_cache[1, 0, 4, :, :3], k[0])
     wide.reset()
     assert wide.get_pos() == 0
+
+
+def test_device_side_decode_and_quantiles_equal_the_host_path():
+    """dgpt_integrate_tokens against the host decode of whole sequences (mixed orders, bit for bit), and the
+    device-side quantiles of DiffGPT.predict_quantiles against np.quantile over predict_samples."""
+    import pandas as pd
+
+    from diff_gpt_b200 import TemperatureSampler, ops
+    from diff_gpt_b200.diff_gpt import DiffGPT, _quantile_of_sorted
+    from diff_gpt_b200.encoder_decoder import _orders, decode, encode, get_domain_of_definition, integrate_end_state
+
+    rng = np.random.default_rng(7)
+    V, F, rows, H, N = 256, 5, 40, 12, 33
+    order = np.array([0, 1, 2, 3, 1])
+    x = np.cumsum(rng.normal(size=(rows, F)), axis=0)
+    dom = get_domain_of_definition(x, order, use_decimal=False)
+    start, scale, enc = encode(inp=x, vocab_size=V, domain_of_definition=dom, order_of_derivative=order, use_decimal=False)
+    gen = rng.integers(0, V, size=(N, H * F))
+    whole = np.concatenate([np.broadcast_to(enc.reshape(1, -1), (N, enc.size)), gen], axis=1).reshape(N, -1, F)
+    want = decode(start=start, scale=scale, inp=whole.astype(np.int64), vocab_size=V, order_of_derivative=order,
+                  use_decimal=False)[:, rows:]
+    state = integrate_end_state(start, (enc - V // 2) / scale, order)
+    sc = np.array(np.broadcast_to(np.asarray(scale, dtype=np.float64).reshape(-1), (F,)))
+    got = ops.integrate_tokens(
+        torch.from_numpy(gen.astype(np.int32)).cuda(), F, V, torch.from_numpy(sc).cuda(),
+        torch.from_numpy(_orders(order, F).astype(np.int32)).cuda(), torch.from_numpy(state).cuda(),
+    )
+    assert got.shape == (N, H, F) and np.array_equal(got.cpu().numpy(), want)
+    srt = torch.sort(got, dim=0).values
+    for q in (0.1, 0.5, 0.9):
+        assert np.array_equal(_quantile_of_sorted(srt, q).cpu().numpy(), np.quantile(want, q, axis=0))
+    # through the facade: same trajectories from predict_samples and inside predict_quantiles (seeded stream)
+    g = load_golden("cfg1_fp32")
+    m = _model(g["meta"], golden_weights(g, torch.float32), torch.float32)
+    dg = DiffGPT(model=m, order_of_derivative=1, domain_of_definition=g["domain"], use_decimal=False)
+    df = pd.DataFrame(g["ctx"], columns=["y"])
+    s = TemperatureSampler(1.0)
+    fut = dg.predict_samples(df, max_new_points=24, num_samples=50, sampler=s)
+    qs = dg.predict_quantiles(df, 24, quantiles=(0.1, 0.5, 0.9), num_samples=50, sampler=s)
+    for q in (0.1, 0.5, 0.9):
+        assert np.array_equal(qs[q].to_numpy(), np.quantile(fut, q, axis=0))
