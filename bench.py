@@ -25,9 +25,7 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
 import time
 
 import numpy as np
@@ -511,6 +509,7 @@ def kernel_case(name: str, iters: int = 8) -> None:
     sample:      config-4 logits, 4096 rows x 4096 tokens, nucleus 0.9.
     depthmix:    config-4 rows, 8 candidates (mid-stack).
     fmha_prefix: shared-prompt phase of a config-4 decode step (4096 rows x 1024 prompt keys, 12 heads x 64).
+    linear:      first feed-forward GEMM of a config-4 decode step with the SwiGLU epilogue.
     Prints one JSON line with the CUDA-event time per launch and the achieved rate.
     """
     from diff_gpt_b200 import ops
@@ -577,6 +576,19 @@ def kernel_case(name: str, iters: int = 8) -> None:
 
         work = 4 * R * P * C
         unit, peak = "TFLOP/s", pk["bf16_tflops"]
+    elif name == "linear":
+        # first feed-forward GEMM of a config-4 decode step with the SwiGLU epilogue: [4096, 768] x [3072, 768]^T -> [4096, 1536]
+        M, K, N = TRAJECTORIES, CFG4["n_embd"], 4 * CFG4["n_embd"]
+        a = torch.randn((M, K), device=dev, dtype=torch.bfloat16, generator=g)
+        wgt = torch.randn((N, K), device=dev, dtype=torch.bfloat16, generator=g) * 0.05
+        act = torch.empty((M, N // 2), device=dev, dtype=torch.bfloat16)
+        st = torch.zeros(1, dtype=torch.int32, device=dev)
+
+        def launch():
+            ops.linear(a, wgt, act, swiglu=(1.702, 7.0), status=st)
+
+        work = 2 * M * N * K
+        unit, peak = "TFLOP/s", pk["bf16_tflops"]
     elif name == "sample":
         R, V = TRAJECTORIES, CFG4["vocab_size"]
         logits = (torch.randn((R, V), device=dev, generator=g) * 0.05).to(torch.bfloat16)  # near-flat, as at random init
@@ -628,7 +640,7 @@ def kernel_case(name: str, iters: int = 8) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel-case", default=None, choices=["decode_attn", "fmha", "fmha_long", "sample", "depthmix", "fmha_prefix"],
+    ap.add_argument("--kernel-case", default=None, choices=["decode_attn", "fmha", "fmha_long", "sample", "depthmix", "fmha_prefix", "linear"],
                     help="run one kernel alone on a small case (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
