@@ -211,6 +211,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
+// The bounded wait by itself: two threads (of two warps) wait on a barrier that only one arrival could complete.  With
+// `arrive` set the first thread arrives and both waits succeed; without it nothing ever arrives, the first
+// wait gives up after `limit_cycles`, raises the flag, the second thread sees the flag and gives up too.
+// out[0], out[1]: 1 where the wait succeeded; out[2]: the flag (the code of the wait that gave up);
+// out[3]: clock cycles the first thread spent.
+__global__ void bounded_wait_probe_kernel(int arrive, long long limit_cycles, int* out) {
+  __shared__ uint64_t bar;
+  __shared__ int flag;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    flag = 0;
+    mbar_init(b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && arrive) mbar_arrive(b);
+  if (threadIdx.x == 0 || threadIdx.x == 32) {  // two warps; the second has a limit it will not reach
+    const int who = threadIdx.x >> 5;
+    const long long t0 = clock64();
+    const bool ok = wait_or_abort(b, 0, &flag, 40 + who, who == 0 ? limit_cycles : 16 * limit_cycles);
+    out[who] = ok ? 1 : 0;
+    if (who == 0) out[3] = (int)min(clock64() - t0, (long long)0x7fffffff);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) out[2] = flag;
+}
+
 // 2-D bf16 tensor map over a row-major [rows, cols] matrix with a [box_rows][64] box, 128-byte swizzle.
 static bool encode_2d(CUtensorMap* map, const void* base, long long rows, long long cols, long long row_stride,
                       int box_rows) {
@@ -232,6 +259,13 @@ static bool encode_2d(CUtensorMap* map, const void* base, long long rows, long l
 }  // namespace dgpt
 
 using namespace dgpt;
+
+extern "C" int dgpt_bounded_wait_probe(int32_t arrive, int64_t limit_cycles, int32_t* out, void* stream) {
+  DGPT_REQUIRE(out, "bounded_wait_probe: NULL pointer");
+  DGPT_REQUIRE(limit_cycles > 0 && limit_cycles <= 2000000000ll, "bounded_wait_probe: limit must be in (0, 2e9] cycles");
+  tc::bounded_wait_probe_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(arrive, limit_cycles, out);
+  return launch_status("bounded_wait_probe");
+}
 
 extern "C" int dgpt_linear(const void* a, int64_t a_row_stride, const void* w, int64_t w_row_stride, void* out,
                            int64_t out_row_stride, const void* resid, int64_t resid_row_stride, int32_t M, int32_t N,

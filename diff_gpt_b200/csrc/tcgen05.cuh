@@ -175,14 +175,15 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 
 // Bounded wait that also gives up early when another thread has raised the CTA's abort flag.
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site = 2) {
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site = 2,
+                                              long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
     for (int i = 0; i < 32; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) break;
+    if (clock64() - t0 > limit_cycles) break;
   }
   *abort_flag = site;  // which wait gave up (reported through the status word)
   return false;

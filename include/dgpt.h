@@ -208,6 +208,14 @@ int dgpt_linear(const void* a, int64_t a_row_stride, const void* w, int64_t w_ro
                 int32_t K, int32_t epilogue, float alpha, float limit, int32_t dtype, int32_t* status,
                 void* stream);
 
+/* The time-bounded mbarrier wait that every tcgen05 kernel of the library uses, run by itself in a one-CTA
+ * kernel (no counterpart in the reference).  Two threads wait on a barrier that needs one arrival.  arrive != 0:
+ * the arrival is made and both waits succeed.  arrive == 0: nothing arrives; the first thread gives up after
+ * limit_cycles SM clock cycles (at most 2e9, about a second) and raises the CTA's abort flag, the second gives
+ * up on seeing the flag; the kernel then returns normally.  out: device int32 [4] = {first wait ok, second wait
+ * ok, code of the wait that gave up (0 if none), cycles the first thread waited}. */
+int dgpt_bounded_wait_probe(int32_t arrive, int64_t limit_cycles, int32_t* out, void* stream);
+
 /* out[r] = log(sum_j exp(logits[r, j])) - logits[r, targets[r]]: the negative log-likelihood of one given
  * token per row, without materialising the log-probabilities.  The log-probability is rounded once to
  * `dtype` as the reference's log_softmax output is.  Replaces the log_softmax + gather of
