@@ -315,12 +315,13 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
 }
 
 // ---- warp-specialised variant ------------------------------------------------------------------
-// 128 softmax threads (one per query row), one warp whose first lane issues every tcgen05.mma and one warp
-// whose first lane issues every TMA load.  Scores and probabilities are double-buffered in TMEM (S0, S1 at columns 0 and 128; P0, P1 as
-// packed bf16 at 256 and 320; O at 384), K and V tiles live in two-deep rings, and all hand-offs are mbarriers:
-//   bar_s[b]  S of a tile is in buffer b            (tcgen05.commit)
-//   bar_p[b]  all 128 rows have written P into b    (128 thread arrivals)
-//   bar_o[b]  the P V product of that tile is done   (tcgen05.commit)
+// 256 softmax threads (two per query row), one warp whose first lane issues every tcgen05.mma and one warp
+// whose first lane issues every TMA load.  Scores and probabilities are double-buffered in TMEM (S0, S1 at
+// columns 0 and 128; P0, P1 as packed bf16 at 256 and 320; O at 384), K tiles live in a ring of three, V tiles
+// in a ring of two, and all hand-offs are mbarriers:
+//   bar_s[b]  S of a tile is in buffer b                     (tcgen05.commit)
+//   bar_p[b]  all 256 softmax threads have written P into b  (256 thread arrivals)
+//   bar_o[b]  the P V product of that tile is done            (tcgen05.commit)
 // so the softmax of tile j overlaps P V of tile j-1 and Q K^T of tile j+1.  One CTA per SM (512 TMEM columns).
 #ifdef DGPT_TC_PROF
 __device__ long long g_prof[16];
