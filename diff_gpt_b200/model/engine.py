@@ -12,7 +12,9 @@ same RoPE-ceiling clamp.  What differs is where the work happens:
     so there is no per-step host synchronisation (the reference reads the tokens
     back and re-uploads them every step, engine.py:121,150);
   * `generate_many` (additive API) decodes several series in one batch and can
-    take a trajectory offset, which is what the multi-GPU sharding uses.
+    take a trajectory offset, which is what the multi-GPU sharding uses;
+  * the page pool, the forward plans and the captured step graph are kept on the
+    engine and reused by the next call of the same shape (`Engine.release()` frees them).
 
 A sampler that is not one of the library's (any callable `f(logits, rng)`) is
 honoured by running the same forward eagerly and handing it the device logits.
