@@ -53,7 +53,7 @@ PROTOTYPES = {
     ),
     "dgpt_fmha_prefill": (
         C.c_int,
-        [_p, _i64, _i64, _kvp, _p, _i32, _p, _i64, _i64, _i32, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _p, _p],
+        [_p, _i64, _i64, _kvp, _p, _i32, _p, _i64, _i64, _i32, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _p, _p],
     ),
     "dgpt_decode_attn_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32]),
     "dgpt_decode_attn": (

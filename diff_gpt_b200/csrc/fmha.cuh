@@ -16,6 +16,7 @@ struct FmhaArgs {
   float* lse;
   int B, H, Tq, D, q_offset, causal, dtype;
   int* status;
+  int max_ctas;  // two-CTAs-per-SM kernel only: at most this many CTAs, looping over the query tiles (0 = one CTA per tile)
   int two_cta;  // tensor-core path only: the 128-thread kernel with two CTAs per SM instead of the warp-specialised one
 };
 

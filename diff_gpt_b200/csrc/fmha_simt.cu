@@ -183,7 +183,7 @@ extern "C" int dgpt_fmha_prefill(const void* q, int64_t q_batch_stride, int64_t 
                                  const dgpt_kv_layout* kv, const int32_t* kv_len, int32_t kv_len_all, void* o,
                                  int64_t o_batch_stride, int64_t o_row_stride, int32_t o_f32, float* lse, int32_t B,
                                  int32_t H, int32_t Tq, int32_t D, int32_t q_offset, int32_t causal, int32_t dtype,
-                                 int32_t impl, int32_t* status, void* stream) {
+                                 int32_t impl, int32_t max_ctas, int32_t* status, void* stream) {
   DGPT_REQUIRE(q && o, "fmha_prefill: NULL pointer");
   DGPT_REQUIRE(B >= 0 && H > 0 && Tq >= 0 && B <= 65535 && H <= 65535, "fmha_prefill: bad sizes");
   DGPT_REQUIRE(kv_len || kv_len_all >= 0, "fmha_prefill: kv length missing");
@@ -199,6 +199,7 @@ extern "C" int dgpt_fmha_prefill(const void* q, int64_t q_batch_stride, int64_t 
   a.o = o; a.o_bs = o_batch_stride; a.o_rs = o_row_stride; a.o_f32 = o_f32; a.lse = lse;
   a.B = B; a.H = H; a.Tq = Tq; a.D = D; a.q_offset = q_offset; a.causal = causal; a.dtype = dtype;
   a.status = status;
+  a.max_ctas = max_ctas;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const KvView view = make_view(kv);
   const bool tc_ok = fmha_tc_supported(a, *kv);

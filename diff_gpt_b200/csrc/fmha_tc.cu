@@ -56,6 +56,7 @@ struct Params {
   int H, Tq, q_offset, causal;
   float scale_log2;
   int* status;
+  int n_qt, n_work;  // query tiles per (batch, head) and work items in all (two-CTAs-per-SM kernel: CTAs loop over them)
 };
 
 template <int D>
@@ -80,16 +81,8 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
   const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int b = blockIdx.z, h = blockIdx.y;
-  const int qt = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;  // long tiles first
-  const int q0 = qt * kBM;
-  const int klen = p.kv_len ? p.kv_len[b] : p.kv_len_all;
-  const int kmax = p.causal ? min(klen, p.q_offset + min(q0 + kBM, p.Tq)) : klen;
-  const int n_tiles = kmax > 0 ? (kmax + kBN - 1) / kBN : 0;
   const int pt = p.page_tokens;
-
-  if (tid == 0) {
-    *abort_flag = 0;
+  auto init_barriers = [&]() {  // thread 0; every phase of the previous work item has completed
     mbar_init(bar_q, 1);
     mbar_init(bar_k, 1);
     mbar_init(bar_v, 1);
@@ -97,6 +90,10 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
     mbar_init(bar_o, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
+  };
+  if (tid == 0) {
+    *abort_flag = 0;
+    init_barriers();
   }
   if (warp == 0) {
     tmem_alloc(smem_u32(tmem_slot), kTmemCols);
@@ -107,6 +104,31 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+  bool fail = false;
+  int pend_k = -1, pend_v = -1, pend_s = -1, pend_o = -1;  // thread 0: parity of an outstanding phase, or -1
+
+  // A CTA takes the work items blockIdx.x, blockIdx.x + gridDim.x, ...  (one each when the grid covers them all;
+  // a smaller grid keeps the kernel on few SMs, which is how the decode step runs it beside the per-row kernel).
+  for (int work = blockIdx.x; work < p.n_work; work += gridDim.x) {
+  if (work != (int)blockIdx.x) {  // barriers start every work item in phase 0
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar_q) : "memory");
+      asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar_k) : "memory");
+      asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar_v) : "memory");
+      asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar_s) : "memory");
+      asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar_o) : "memory");
+      init_barriers();
+    }
+    __syncthreads();
+  }
+  const int qt_idx = work % p.n_qt, bh = work / p.n_qt;
+  const int h = bh % p.H, b = bh / p.H;
+  const int qt = p.causal ? p.n_qt - 1 - qt_idx : qt_idx;  // long tiles first
+  const int q0 = qt * kBM;
+  const int klen = p.kv_len ? p.kv_len[b] : p.kv_len_all;
+  const int kmax = p.causal ? min(klen, p.q_offset + min(q0 + kBM, p.Tq)) : klen;
+  const int n_tiles = kmax > 0 ? (kmax + kBN - 1) / kBN : 0;
 
   // Issue the TMA loads of key/value tile j (thread 0 only).  One box per page and per 64-wide half.
   auto load_kv = [&](const CUtensorMap* map, uint32_t dst, uint32_t bar, int j) {
@@ -132,8 +154,6 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
   };
 
   float m = -INFINITY, l = 0.f;
-  bool fail = false;
-  int pend_k = -1, pend_v = -1, pend_s = -1, pend_o = -1;  // thread 0: parity of an outstanding phase, or -1
 
   if (tid == 0 && n_tiles > 0) {
     mbar_expect_tx(bar_q, kTileBytes);
@@ -301,14 +321,19 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
       }
     }
     if (row_ok && p.lse) p.lse[((long long)b * p.Tq + qi) * p.H + h] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
-  } else if (tid == 0) {
-    // a wait ran out: record it, then give whatever is still in flight a bounded chance to land
-    if (p.status) atomicExch(p.status, 2);
-    if (pend_k >= 0) mbar_wait(bar_k, (uint32_t)pend_k);
-    if (pend_v >= 0) mbar_wait(bar_v, (uint32_t)pend_v);
-    if (pend_s >= 0) mbar_wait(bar_s, (uint32_t)pend_s);
-    if (pend_o >= 0) mbar_wait(bar_o, (uint32_t)pend_o);
+    tc_fence_before();  // the next work item's MMAs overwrite the TMEM columns just read
+  } else {
+    if (tid == 0) {
+      // a wait ran out: record it, then give whatever is still in flight a bounded chance to land
+      if (p.status) atomicExch(p.status, 2);
+      if (pend_k >= 0) mbar_wait(bar_k, (uint32_t)pend_k);
+      if (pend_v >= 0) mbar_wait(bar_v, (uint32_t)pend_v);
+      if (pend_s >= 0) mbar_wait(bar_s, (uint32_t)pend_s);
+      if (pend_o >= 0) mbar_wait(bar_o, (uint32_t)pend_o);
+    }
+    break;  // CTA-uniform: `fail` left the tile loop through __syncthreads_or
   }
+  }  // work items
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
@@ -791,7 +816,9 @@ int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
   p.causal = a.causal;
   p.scale_log2 = kLog2e / sqrtf((float)D);
   p.status = a.status;
-  dim3 grid((unsigned)((a.Tq + kBM - 1) / kBM), (unsigned)a.H, (unsigned)a.B);
+  p.n_qt = (a.Tq + kBM - 1) / kBM;
+  p.n_work = p.n_qt * a.H * a.B;
+  dim3 grid((unsigned)p.n_qt, (unsigned)a.H, (unsigned)a.B);
   // >= 80 KB per CTA keeps residency at two CTAs per SM, which is what the 2 x 256 TMEM columns allow
   size_t smem = (size_t)3 * (D / 64) * kBN * 128 + 64 + 1024;
   if (smem < 80 * 1024) smem = 80 * 1024;
@@ -813,12 +840,14 @@ int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
     }
     return launch_status("fmha_tc_ws");
   }
+  // one CTA per work item, or fewer CTAs that loop over the items when the caller wants the kernel on few SMs
+  const unsigned n_cta = (a.max_ctas > 0 && a.max_ctas < p.n_work) ? (unsigned)a.max_ctas : (unsigned)p.n_work;
   if (D == 64) {
     e = cudaFuncSetAttribute(fmha_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) fmha_tc_kernel<64><<<grid, 128, smem, st>>>(mq, mk, mv, p);
+    if (e == cudaSuccess) fmha_tc_kernel<64><<<n_cta, 128, smem, st>>>(mq, mk, mv, p);
   } else {
     e = cudaFuncSetAttribute(fmha_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) fmha_tc_kernel<128><<<grid, 128, smem, st>>>(mq, mk, mv, p);
+    if (e == cudaSuccess) fmha_tc_kernel<128><<<n_cta, 128, smem, st>>>(mq, mk, mv, p);
   }
   if (e != cudaSuccess) {
     set_error("fmha_tc: cudaFuncSetAttribute: %s", cudaGetErrorString(e));

@@ -106,6 +106,10 @@ class Block(nn.Module):
 
 FUSED_FFN = True  # first feed-forward GEMM on the library's tcgen05 kernel with the SwiGLU fused (bf16 only)
 FUSED_FFN_MIN_ROWS = 256
+# Cap on the CTAs of the shared-prompt attention phase while it runs beside the per-row phase: None = one per SM
+# (two per SM, the kernel's own residency, leave no registers for the per-row kernel: 1270 against 1250 ms per
+# 255 config-4 steps; caps below ~100 make this phase the longer one), 0 = no cap.
+PREFIX_CTAS = None
 SIDE_PRIORITY = -1  # stream of the shared-prompt attention phase: ahead of the per-row phase it runs beside
 
 
@@ -175,6 +179,7 @@ class ForwardPlan:
         self.part_o = None
         self.part_lse = None
         self.side = None
+        self.prefix_ctas = 0
         self.workspace = None
 
     def _decode_extras(self, b: KvBinding) -> None:
@@ -188,6 +193,9 @@ class ForwardPlan:
             self.part_o = torch.empty((self.n, H, D), dtype=torch.float32, device=dev)
             self.part_lse = torch.empty((self.n, H), dtype=torch.float32, device=dev)
             self.side = torch.cuda.Stream(device=dev, priority=SIDE_PRIORITY)
+            self.prefix_ctas = (
+                torch.cuda.get_device_properties(dev).multi_processor_count if PREFIX_CTAS is None else PREFIX_CTAS
+            )
         if b.n_splits > 1 and self.workspace is None:
             nbytes = ops.decode_attn_workspace_bytes(self.n, H, D, b.n_splits)
             self.workspace = torch.empty(nbytes // 4, dtype=torch.float32, device=dev)
@@ -227,6 +235,7 @@ class ForwardPlan:
                         self.q, b.shared_layouts[i], self.prefix_o, B=n_seq // N, H=H, Tq=N, D=D,
                         q_batch_stride=N * C, q_row_stride=C, o_batch_stride=N * C, o_row_stride=C,
                         kv_len=b.shared_len, causal=False, lse=self.prefix_lse, impl=b.fmha_impl, status=self.status,
+                        max_ctas=self.prefix_ctas if self.side is not None else 0,
                     )
                     po, pl = self.prefix_o, self.prefix_lse
                 if po is not None and self.side is not None:

@@ -136,6 +136,7 @@ def fmha_prefill(
     lse: torch.Tensor | None = None,
     impl: int = 0,
     status: torch.Tensor | None = None,
+    max_ctas: int = 0,
 ) -> None:
     _cuda(q, o, kv_len, lse, status)
     o_f32 = int(o.dtype == torch.float32 and q.dtype != torch.float32)
@@ -143,7 +144,7 @@ def fmha_prefill(
         lib.dgpt_fmha_prefill(
             q.data_ptr(), q_batch_stride, q_row_stride, C.byref(kv), _ptr(kv_len), kv_len_all, o.data_ptr(),
             o_batch_stride, o_row_stride, o_f32, _ptr(lse), B, H, Tq, D, q_offset, int(causal), dtype_code(q),
-            impl, _ptr(status), _stream(),
+            impl, max_ctas, _ptr(status), _stream(),
         )
     )
 

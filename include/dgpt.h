@@ -111,12 +111,14 @@ int dgpt_rope_qknorm_kvappend(const void* q, const void* k, const void* v, int64
  * the warp-level online-softmax kernel; of the two tensor-core kernels the warp-specialised one is taken
  * from 4096 keys on, the two-CTAs-per-SM one below), 1 = warp-level kernel, 2 = warp-specialised
  * tensor-core kernel or fail, 3 = tensor-core kernel with two CTAs per SM or fail.
+ * max_ctas: 0, or a cap on the CTAs of the two-CTAs-per-SM kernel, which then loop over the query tiles - for a
+ * caller that runs the kernel on a second stream and wants it to stay on part of the GPU (ignored elsewhere).
  * status: device int32, set non-zero if a bounded wait inside the tensor-core kernel ran out. */
 int dgpt_fmha_prefill(const void* q, int64_t q_batch_stride, int64_t q_row_stride,
                       const dgpt_kv_layout* kv, const int32_t* kv_len, int32_t kv_len_all, void* o,
                       int64_t o_batch_stride, int64_t o_row_stride, int32_t o_f32, float* lse,
                       int32_t B, int32_t H, int32_t Tq, int32_t D, int32_t q_offset, int32_t causal,
-                      int32_t dtype, int32_t impl, int32_t* status, void* stream);
+                      int32_t dtype, int32_t impl, int32_t max_ctas, int32_t* status, void* stream);
 
 /* Bytes of workspace dgpt_decode_attn needs for R rows, H heads, head_dim D and n_splits. */
 size_t dgpt_decode_attn_workspace_bytes(int32_t R, int32_t H, int32_t D, int32_t n_splits);

@@ -86,3 +86,32 @@ def test_paged_ragged_offset(D, pt, impl):
 def test_matches_warp_level_kernel_on_a_long_causal_case(impl):
     _run(128, B=1, H=2, Tq=1024, Tk=[1024], pt=1024, causal=True, q_offset=0, use_table=False, o_f32=False, impl=impl)
     _run(64, B=1, H=2, Tq=640, Tk=[1024], pt=64, causal=True, q_offset=384, use_table=True, o_f32=False, impl=impl)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_capped_grid_loops_over_query_tiles_with_identical_results(D, causal):
+    """impl 3 with max_ctas below the number of (query tile, head, batch) items: every CTA walks several items
+    (barriers re-initialised in between) and the output is bit-identical to one CTA per item."""
+    from diff_gpt_b200 import ops
+
+    B, H, Tq, Tk, pt = 2, 3, 600, 700, 64
+    g = torch.Generator(device="cuda").manual_seed(D + causal)
+    q = torch.randn((B, Tq, H, D), device="cuda", dtype=torch.bfloat16, generator=g)
+    pages = -(-Tk // pt)
+    pool = torch.randn((B * pages, 2, H, pt, D), device="cuda", dtype=torch.bfloat16, generator=g)
+    table = torch.randperm(B * pages, generator=torch.Generator().manual_seed(1)).to(torch.int32).view(B, pages).cuda()
+    lay = ops.kv_layout(pool[0, 0], pool[0, 1], 2 * H * pt * D, pt * D, pt, table, n_pages=B * pages)
+    klen = torch.tensor([Tk, Tk - 77], dtype=torch.int32, device="cuda")
+    outs = []
+    for cap in (0, 1, 7, 1000):
+        o = torch.full((B, Tq, H, D), float("nan"), device="cuda", dtype=torch.float32)
+        lse = torch.full((B, Tq, H), float("nan"), device="cuda", dtype=torch.float32)
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ops.fmha_prefill(q, lay, o, B=B, H=H, Tq=Tq, D=D, q_batch_stride=Tq * H * D, q_row_stride=H * D,
+                         o_batch_stride=Tq * H * D, o_row_stride=H * D, kv_len=klen, q_offset=Tk - 77 - Tq if causal else 0,
+                         causal=causal, lse=lse, impl=3, status=status, max_ctas=cap)
+        assert status.item() == 0 and torch.isfinite(o).all() and torch.isfinite(lse).all()
+        outs.append((o, lse))
+    for o, lse in outs[1:]:
+        assert torch.equal(o, outs[0][0]) and torch.equal(lse, outs[0][1])
