@@ -385,16 +385,10 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
                  bar_kf0 = bar_q + 96;  // K slot released (its S product has been computed)
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int b = blockIdx.z, h = blockIdx.y;
-  const int qt = p.causal ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
-  const int q0 = qt * kBM;
-  const int klen = p.kv_len ? p.kv_len[b] : p.kv_len_all;
-  const int kmax = p.causal ? min(klen, p.q_offset + min(q0 + kBM, p.Tq)) : klen;
-  const int n_tiles = kmax > 0 ? (kmax + kBN - 1) / kBN : 0;
   const int pt = p.page_tokens;
-
-  if (tid == 0) {
-    *abort_flag = 0;
+  auto init_barriers = [&](bool again) {  // thread 0; `again`: every phase of the previous work item has completed
+    if (again)
+      for (int i = 0; i < 15; ++i) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar_q + 8 * i) : "memory");
     mbar_init(bar_q, 1);
     mbar_init(bar_k0 + 16, 1);
     for (int i = 0; i < 3; ++i) mbar_init(bar_kf0 + 8 * i, 1);
@@ -407,6 +401,10 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
+  };
+  if (tid == 0) {
+    *abort_flag = 0;
+    init_barriers(false);
   }
   if (tid < 2 * kBM) {  // turn numbers of a previous CTA on this SM must not be mistaken for this one's
     xch[tid] = 0ull;
@@ -420,6 +418,32 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+
+  // A CTA takes the work items (query tile, head, batch) cta, cta + n_cta, ...: one each when the grid covers them
+  // all; a smaller grid (max_ctas) keeps the kernel on part of the GPU.  Barriers and hand-over words start every
+  // item afresh, so the per-item code below can derive every phase from the tile index.
+  const int n_cta = (int)(gridDim.x * gridDim.y * gridDim.z);
+  const int cta = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+  for (int work = cta; work < p.n_work; work += n_cta) {
+  if (work != cta) {
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) break;  // a wait ran out in the previous item: the roles have drained, leave together
+    if (tid == 0) init_barriers(true);
+    if (tid < 2 * kBM) {
+      xch[tid] = 0ull;
+      xch[2 * kBM + tid] = 0ull;
+    }
+    __syncthreads();
+    tc_fence_after();
+  }
+  const int qt_idx = work % p.n_qt, bh = work / p.n_qt;
+  const int h = bh % p.H, b = bh / p.H;
+  const int qt = p.causal ? p.n_qt - 1 - qt_idx : qt_idx;  // long tiles first
+  const int q0 = qt * kBM;
+  const int klen = p.kv_len ? p.kv_len[b] : p.kv_len_all;
+  const int kmax = p.causal ? min(klen, p.q_offset + min(q0 + kBM, p.Tq)) : klen;
+  const int n_tiles = kmax > 0 ? (kmax + kBN - 1) / kBN : 0;
   bool fail = false;
 
   if (warp == 9) {
@@ -735,6 +759,7 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       atomicExch(p.status, *abort_flag ? *abort_flag : 2);
     }
   }
+  }  // work items
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kWsTmemCols);
@@ -827,12 +852,13 @@ int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
     // warp-specialised kernel: Q + two K + two V tiles, padded so that one CTA owns an SM (it allocates all 512 TMEM columns)
     size_t ws_smem = (size_t)6 * (D / 64) * kBN * 128 + 8192 + 1024;  // tiles, barriers and exchange area, alignment slack
     if (ws_smem < 120 * 1024) ws_smem = 120 * 1024;
+    const dim3 ws_grid = (a.max_ctas > 0 && a.max_ctas < p.n_work) ? dim3((unsigned)a.max_ctas) : grid;
     if (D == 64) {
       e = cudaFuncSetAttribute(fmha_tc_ws_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ws_smem);
-      if (e == cudaSuccess) fmha_tc_ws_kernel<64><<<grid, kWsThreads, ws_smem, st>>>(mq, mk, mv, p);
+      if (e == cudaSuccess) fmha_tc_ws_kernel<64><<<ws_grid, kWsThreads, ws_smem, st>>>(mq, mk, mv, p);
     } else {
       e = cudaFuncSetAttribute(fmha_tc_ws_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ws_smem);
-      if (e == cudaSuccess) fmha_tc_ws_kernel<128><<<grid, kWsThreads, ws_smem, st>>>(mq, mk, mv, p);
+      if (e == cudaSuccess) fmha_tc_ws_kernel<128><<<ws_grid, kWsThreads, ws_smem, st>>>(mq, mk, mv, p);
     }
     if (e != cudaSuccess) {
       set_error("fmha_tc: cudaFuncSetAttribute: %s", cudaGetErrorString(e));

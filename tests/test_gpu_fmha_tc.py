@@ -90,9 +90,10 @@ def test_matches_warp_level_kernel_on_a_long_causal_case(impl):
 
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("causal", [False, True])
-def test_capped_grid_loops_over_query_tiles_with_identical_results(D, causal):
-    """impl 3 with max_ctas below the number of (query tile, head, batch) items: every CTA walks several items
-    (barriers re-initialised in between) and the output is bit-identical to one CTA per item."""
+@pytest.mark.parametrize("impl", IMPLS)
+def test_capped_grid_loops_over_query_tiles_with_identical_results(D, causal, impl):
+    """max_ctas below the number of (query tile, head, batch) items: every CTA walks several items (barriers
+    re-initialised in between) and the output is bit-identical to one CTA per item, for both tensor-core kernels."""
     from diff_gpt_b200 import ops
 
     B, H, Tq, Tk, pt = 2, 3, 600, 700, 64
@@ -110,7 +111,7 @@ def test_capped_grid_loops_over_query_tiles_with_identical_results(D, causal):
         status = torch.zeros(1, dtype=torch.int32, device="cuda")
         ops.fmha_prefill(q, lay, o, B=B, H=H, Tq=Tq, D=D, q_batch_stride=Tq * H * D, q_row_stride=H * D,
                          o_batch_stride=Tq * H * D, o_row_stride=H * D, kv_len=klen, q_offset=Tk - 77 - Tq if causal else 0,
-                         causal=causal, lse=lse, impl=3, status=status, max_ctas=cap)
+                         causal=causal, lse=lse, impl=impl, status=status, max_ctas=cap)
         assert status.item() == 0 and torch.isfinite(o).all() and torch.isfinite(lse).all()
         outs.append((o, lse))
     for o, lse in outs[1:]:
