@@ -42,8 +42,12 @@ __device__ __forceinline__ void merge_partial(float& m, float& l, float* acc, fl
 #define DGPT_DEC_MINB 4     // minimum resident CTAs per SM asked of the compiler
 #endif
 
-template <typename T, int D>
-__global__ void __launch_bounds__(128, DGPT_DEC_MINB)
+// U = 16-byte loads in flight per lane and tensor, MINB = resident CTAs per SM asked of the compiler.  (8, 4) is the
+// fastest form of the kernel by itself (99 % of the copy bandwidth); (4, 8) needs half the registers per CTA and is
+// what the decode step uses while the shared-prompt kernel occupies part of every SM (1259 against 1272 ms per 255
+// config-4 steps, although by itself it reaches 95 %).
+template <typename T, int D, int U_, int MINB_>
+__global__ void __launch_bounds__(128, MINB_)
 decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const int* __restrict__ len0,
                    const int* __restrict__ start1, const int* __restrict__ len1, const int* __restrict__ step_ptr,
                    const float* __restrict__ prefix_o, const float* __restrict__ prefix_lse,
@@ -80,7 +84,7 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
 
   const T* kbase = static_cast<const T*>(kv.k);
   const T* vbase = static_cast<const T*>(kv.v);
-  constexpr int U = DGPT_DEC_U;
+  constexpr int U = U_;
   // Walk the keys page by page: one page-table lookup per page, then a dense run of tokens.
   for (int i = begin; i < end;) {  // every quantity below is warp-uniform
     const bool in0 = i < n0;
@@ -291,9 +295,14 @@ static int decode_launch(const void* q, long long q_stride, const KvView& kv, co
   float* ws_o = ws ? ws + 2 * RH * n_splits : nullptr;
   const float scale_log2 = kLog2e / sqrtf((float)D);
   dim3 grid((unsigned)((RH + 3) / 4), (unsigned)n_splits);
-  launch_dep(decode_attn_kernel<T, D>, grid, dim3(128), 0, st, static_cast<const T*>(q), q_stride, kv, len0, start1, len1,
-             step_ptr, prefix_o, prefix_lse, static_cast<const T*>(gate), gate_stride, static_cast<T*>(y), y_stride, ws_ml,
-             ws_o, part_o, part_lse, n_splits, R, H, scale_log2);
+  if (part_lse)  // runs beside the shared-prompt kernel: the lighter form
+    launch_dep(decode_attn_kernel<T, D, DGPT_DEC_U / 2, DGPT_DEC_MINB * 2>, grid, dim3(128), 0, st, static_cast<const T*>(q),
+               q_stride, kv, len0, start1, len1, step_ptr, prefix_o, prefix_lse, static_cast<const T*>(gate), gate_stride,
+               static_cast<T*>(y), y_stride, ws_ml, ws_o, part_o, part_lse, n_splits, R, H, scale_log2);
+  else
+    launch_dep(decode_attn_kernel<T, D, DGPT_DEC_U, DGPT_DEC_MINB>, grid, dim3(128), 0, st, static_cast<const T*>(q),
+               q_stride, kv, len0, start1, len1, step_ptr, prefix_o, prefix_lse, static_cast<const T*>(gate), gate_stride,
+               static_cast<T*>(y), y_stride, ws_ml, ws_o, part_o, part_lse, n_splits, R, H, scale_log2);
   if (int e = launch_status("decode_attn")) return e;
   if (n_splits > 1) {
     const long long n = RH * D;
