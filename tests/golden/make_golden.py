@@ -296,7 +296,9 @@ def anomaly(ref):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref = sys.argv[1]
     sys.path.insert(0, os.path.join(ref, "src"))
     sys.dont_write_bytecode = True
     torch.set_num_threads(4)
