@@ -506,3 +506,23 @@ def test_device_side_decode_and_quantiles_equal_the_host_path():
     qs = dg.predict_quantiles(df, 24, quantiles=(0.1, 0.5, 0.9), num_samples=50, sampler=s)
     for q in (0.1, 0.5, 0.9):
         assert np.array_equal(qs[q].to_numpy(), np.quantile(fut, q, axis=0))
+
+
+def test_gpt_generate_without_cache_matches_the_engine_under_argmax():
+    """GPT.generate (the reference's cache-free sliding-window loop, gpt.py:202-237) and the KV-cache engine produce
+    the same argmax continuation while the window has not started to slide; beyond block_size it keeps going."""
+    from diff_gpt_b200 import Engine, TemperatureSampler
+
+    g = load_golden("small_bf16_d32")
+    w = golden_weights(g, torch.float32)
+    m = _model(g["meta"], w, torch.float32)
+    prompt = g["idx"][0].tolist()
+    room = m.block_size - len(prompt)
+    out = m.generate(torch.tensor([prompt], device="cuda"), room, TemperatureSampler(0.0))
+    assert out.shape == (1, m.block_size) and out[0, : len(prompt)].tolist() == prompt
+    res, _ = Engine(m).generate_batch(prompt, num_samples=1, max_tokens=room, sampler=TemperatureSampler(0.0))
+    assert out[0].tolist() == res[0]
+    ref, _, _ = ref_decode.mc_decode(_shape(g["meta"]), w, prompt, 1, room, temperature=0.0)
+    assert out[0, len(prompt) :].tolist() == ref[0].tolist()
+    longer = m.generate(torch.tensor([prompt], device="cuda"), room + 5, TemperatureSampler(1.0), seed=3)
+    assert longer.shape == (1, m.block_size + 5) and int(longer.min()) >= 0 and int(longer.max()) < m.vocab_size
