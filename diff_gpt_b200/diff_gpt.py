@@ -40,13 +40,21 @@ def _quantile_of_sorted(ordered: torch.Tensor, q: float) -> torch.Tensor:
 
 
 class DiffGPT:
-    __slots__ = ("model", "order_of_derivative", "domain_of_definition", "use_decimal")
+    __slots__ = ("model", "order_of_derivative", "domain_of_definition", "use_decimal", "_engine")
 
     def __init__(self, model: BaseGPT, order_of_derivative, domain_of_definition: np.ndarray, use_decimal: bool) -> None:
         self.model = model
         self.order_of_derivative = order_of_derivative
         self.domain_of_definition = domain_of_definition
         self.use_decimal = use_decimal
+        self._engine = None
+
+    def _get_engine(self) -> Engine:
+        """One Engine per DiffGPT (the reference builds one per call, diff_gpt.py:229,479): the engine keeps its
+        decode state, so repeated forecasts of one shape reuse the page pool and the captured step graph."""
+        if self._engine is None or self._engine.model is not self.model:
+            self._engine = Engine(model=self.model)
+        return self._engine
 
     # ---- helpers ---------------------------------------------------------------------
     def _max_order(self, n_cols: int, label: str) -> int:
@@ -101,7 +109,7 @@ class DiffGPT:
         columns = df.shape[1]
         start, scale, encoded = self._encode(df.to_numpy(dtype=np.float64))
         prompt = encoded.reshape(-1).astype(np.int64).tolist()  # row-major: (time, channel)
-        generated, _ = Engine(model=self.model).generate_many([prompt], num_samples, max_new_points * columns, sampler)
+        generated, _ = self._get_engine().generate_many([prompt], num_samples, max_new_points * columns, sampler)
         V = self.model.vocab_size
         scale_cols = np.array(np.broadcast_to(np.asarray(scale, dtype=np.float64).reshape(-1), (columns,)))  # a writable copy
         state = integrate_end_state(start, (encoded - V // 2) / scale, self.order_of_derivative)
@@ -120,7 +128,7 @@ class DiffGPT:
             return self._future_samples_on_device(df, max_new_points, sampler, num_samples).cpu().numpy()
         start, scale, encoded = self._encode(df.to_numpy(dtype=np.float64))
         prompt = encoded.reshape(-1).astype(np.int64).tolist()  # row-major: (time, channel)
-        results, _ = Engine(model=self.model).generate_batch(
+        results, _ = self._get_engine().generate_batch(
             tokens=prompt, num_samples=num_samples, max_tokens=max_new_points * columns, sampler=sampler
         )
         tokens = np.asarray(results, dtype=np.int64).reshape(num_samples, -1, columns)
@@ -207,7 +215,7 @@ class DiffGPT:
         flat = encoded.reshape(-1).astype(np.int64)
         n_prompt = (ctx_len - max_order) * n_features
         schedule = [None if (p % n_features) in targets else int(flat[p]) for p in range(n_prompt, total_tokens)]
-        results, _ = Engine(model=self.model).generate_batch(
+        results, _ = self._get_engine().generate_batch(
             tokens=flat[:n_prompt].tolist(), num_samples=1, max_tokens=total_tokens - n_prompt, sampler=sampler,
             force_schedule=schedule,
         )
