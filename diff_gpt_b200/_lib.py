@@ -47,6 +47,7 @@ PROTOTYPES = {
     "dgpt_version": (C.c_int, []),
     "dgpt_embed_rmsnorm": (C.c_int, [_p, _p, _p, _i64, _i32, _i32, _i32, _p]),
     "dgpt_depthmix": (C.c_int, [C.POINTER(_p), _i32, _p, _p, _p, _i64, _i32, _i32, _p]),
+    "dgpt_depthmix_cached": (C.c_int, [C.POINTER(_p), C.POINTER(_p), _i32, _p, _p, _p, _p, _i32, _i64, _i32, _i32, _p]),
     "dgpt_rope_qknorm_kvappend": (
         C.c_int,
         [_p, _p, _p, _i64, _p, _i64, _p, _i32, _kvp, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _p, _p],

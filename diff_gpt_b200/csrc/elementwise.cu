@@ -61,6 +61,7 @@ constexpr int kMaxCands = 64;
 struct CandPtrs {
   const void* p[kMaxCands];
   unsigned char mult[kMaxCands];  // how many times the candidate occurs in the caller's list (read once, weighted)
+  const float* inv[kMaxCands];    // rsqrt(mean(cand^2) + eps) per row from an earlier mix over the same data, or NULL
 };
 
 // One warp per row, one pass over the candidates with an online softmax across
@@ -140,7 +141,7 @@ __global__ void depthmix_kernel(CandPtrs cands, int n_cands, const T* __restrict
 template <typename T, int NV>
 __global__ void __launch_bounds__(128, 4)
 depthmix_vec_kernel(CandPtrs cands, int n_cands, const T* __restrict__ w, T* __restrict__ out_h,
-                    T* __restrict__ out_rn, long long rows, int C) {
+                    T* __restrict__ out_rn, float* __restrict__ inv_out, int inv_out_index, long long rows, int C) {
   constexpr int VEC = Io<T>::kVec16;
   constexpr int E = NV * VEC;
   dep_wait();
@@ -164,7 +165,9 @@ depthmix_vec_kernel(CandPtrs cands, int n_cands, const T* __restrict__ w, T* __r
 #endif
   constexpr int AHEAD = DGPT_MIX_AHEAD;
   uint4 nxt[AHEAD][NV];
+  float inv_nxt = 0.f;  // the cached norm factor of the candidate in nxt[0], when it has one (AHEAD == 1)
   auto fetch = [&](int n, uint4* dst) {
+    if (AHEAD == 1 && cands.inv[n]) inv_nxt = cands.inv[n][row];
     const T* src = static_cast<const T*>(cands.p[n]) + row * C;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -177,6 +180,8 @@ depthmix_vec_kernel(CandPtrs cands, int n_cands, const T* __restrict__ w, T* __r
     if (a < n_cands) fetch(a, nxt[a]);
   for (int n = 0; n < n_cands; ++n) {
     float v[E];
+    const bool cached = AHEAD == 1 && cands.inv[n] != nullptr;  // warp-uniform
+    const float inv_cached = inv_nxt;
 #pragma unroll
     for (int i = 0; i < NV; ++i) unpack16<T>(nxt[0][i], v + i * VEC);
 #pragma unroll
@@ -194,19 +199,36 @@ depthmix_vec_kernel(CandPtrs cands, int n_cands, const T* __restrict__ w, T* __r
     // logit = rms_norm(v) . w = rsqrt(mean(v^2) + eps) * (v . w): both sums in one sweep and one
     // interleaved butterfly.  (The reference rounds rms_norm(v) to the storage type before the
     // product; for bf16 that changes the logit by ~1e-4 of its own rounding step.)
+    // A committed candidate does not change between mixes, so its norm factor is computed by the first mix that
+    // sees it and handed to the later ones: they skip the sum of squares and its half of the butterfly.  The
+    // factor is the same number either way (same code computed it), so results do not depend on the cache.
     float s4[4] = {0.f, 0.f, 0.f, 0.f}, d4[4] = {0.f, 0.f, 0.f, 0.f};
+    float inv;
+    float dr;
+    if (cached) {
 #pragma unroll
-    for (int x = 0; x < E; ++x) {
-      s4[x & 3] += v[x] * v[x];
-      d4[x & 3] += v[x] * wv[x];
-    }
-    float ss = (s4[0] + s4[1]) + (s4[2] + s4[3]), dr = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      for (int x = 0; x < E; ++x) d4[x & 3] += v[x] * wv[x];
+      dr = (d4[0] + d4[1]) + (d4[2] + d4[3]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      dr += __shfl_xor_sync(0xffffffffu, dr, o);
+      for (int o = 16; o > 0; o >>= 1) dr += __shfl_xor_sync(0xffffffffu, dr, o);
+      inv = inv_cached;
+    } else {
+#pragma unroll
+      for (int x = 0; x < E; ++x) {
+        s4[x & 3] += v[x] * v[x];
+        d4[x & 3] += v[x] * wv[x];
+      }
+      float ss = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+      dr = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        dr += __shfl_xor_sync(0xffffffffu, dr, o);
+      }
+      inv = rsqrtf(ss / (float)C + kRmsEps);
+      if (n == inv_out_index && lane == 0) inv_out[row] = inv;
     }
-    const float dot = Io<T>::round(dr * rsqrtf(ss / (float)C + kRmsEps));
+    const float dot = Io<T>::round(dr * inv);
     if (dot > m) {  // warp-uniform: the accumulator is rescaled only when the running maximum moves
       const float resc = __expf(m - dot);
       l *= resc;
@@ -248,15 +270,20 @@ static bool depthmix_vec_ok(const CandPtrs& cp, int n, const void* w, void* out_
 }
 
 template <typename T>
-static int depthmix_launch(const CandPtrs& cp, int n, const void* w, void* out_h, void* out_rn,
-                           long long rows, int C, cudaStream_t st) {
+static int depthmix_launch(const CandPtrs& cp, int n, const void* w, void* out_h, void* out_rn, float* inv_out,
+                           int inv_out_index, bool uses_cache, long long rows, int C, cudaStream_t st) {
   const int warps = 4;
   const unsigned grid = (unsigned)((rows + warps - 1) / warps);
-  if (depthmix_vec_ok<T>(cp, n, w, out_h, out_rn, C)) {
+  const bool vec = depthmix_vec_ok<T>(cp, n, w, out_h, out_rn, C);
+  if (uses_cache && !vec) {
+    set_error("depthmix: cached norm factors need 16-byte aligned rows of a multiple of %d elements", Io<T>::kVec16);
+    return DGPT_E_UNSUPPORTED;
+  }
+  if (vec) {
     const int nv = (C / Io<T>::kVec16 + 31) / 32;
 #define DGPT_MIXV(N)                                                                              \
   launch_dep(depthmix_vec_kernel<T, N>, dim3(grid), dim3(warps * 32), 0, st, cp, n, static_cast<const T*>(w), \
-             static_cast<T*>(out_h), static_cast<T*>(out_rn), rows, C)
+             static_cast<T*>(out_h), static_cast<T*>(out_rn), inv_out, inv_out_index, rows, C)
     if (nv <= 1) DGPT_MIXV(1);
     else if (nv <= 2) DGPT_MIXV(2);
     else if (nv <= 3) DGPT_MIXV(3);
@@ -388,34 +415,51 @@ int dgpt_embed_rmsnorm(const int32_t* ids, const void* emb, void* out, int64_t n
   return launch_status("embed_rmsnorm");
 }
 
-int dgpt_depthmix(const void* const* cands, int32_t n_cands, const void* w, void* out_h, void* out_rn,
-                  int64_t rows, int32_t C, int32_t dtype, void* stream) {
+int dgpt_depthmix_cached(const void* const* cands, const float* const* cand_inv, int32_t n_cands, const void* w,
+                         void* out_h, void* out_rn, float* inv_out, int32_t inv_out_index, int64_t rows, int32_t C,
+                         int32_t dtype, void* stream) {
   DGPT_REQUIRE(cands && n_cands >= 1 && n_cands <= kMaxCands, "depthmix: n_cands must be in [1, %d]", kMaxCands);
   DGPT_REQUIRE(n_cands == 1 || w, "depthmix: pseudo-query w is NULL");
   DGPT_REQUIRE(out_h || out_rn, "depthmix: no output requested");
   DGPT_REQUIRE(rows >= 0 && C > 0, "depthmix: bad sizes");
+  DGPT_REQUIRE(inv_out == nullptr || (inv_out_index >= 0 && inv_out_index < n_cands),
+               "depthmix: inv_out_index must name a candidate");
+  DGPT_REQUIRE(inv_out == nullptr || cand_inv == nullptr || cand_inv[inv_out_index] == nullptr,
+               "depthmix: the candidate whose norm factor is to be written must not have one passed in");
   if (rows == 0) return DGPT_OK;
   // A candidate listed several times (the reference commits the embedding twice) is read once and its
   // softmax weight multiplied: p v + p v = 2 p v exactly.
   CandPtrs cp;
-  int n_unique = 0;
+  int n_unique = 0, out_index = -1;
+  bool uses_cache = inv_out != nullptr;
   for (int i = 0; i < n_cands; ++i) {
     DGPT_REQUIRE(cands[i], "depthmix: candidate %d is NULL", i);
     int j = 0;
     while (j < n_unique && cp.p[j] != cands[i]) ++j;
     if (j == n_unique) {
       cp.p[n_unique] = cands[i];
+      cp.inv[n_unique] = cand_inv ? cand_inv[i] : nullptr;
+      uses_cache = uses_cache || cp.inv[n_unique] != nullptr;
       cp.mult[n_unique++] = 1;
     } else {
       ++cp.mult[j];
     }
+    if (inv_out && i == inv_out_index) out_index = j;
   }
   n_cands = n_unique;
+  if (n_cands == 1) out_index = -1;  // a single candidate is passed through: no norm factor is formed
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == DGPT_F32) return depthmix_launch<float>(cp, n_cands, w, out_h, out_rn, rows, C, st);
-  if (dtype == DGPT_BF16) return depthmix_launch<__nv_bfloat16>(cp, n_cands, w, out_h, out_rn, rows, C, st);
+  if (dtype == DGPT_F32)
+    return depthmix_launch<float>(cp, n_cands, w, out_h, out_rn, inv_out, out_index, uses_cache, rows, C, st);
+  if (dtype == DGPT_BF16)
+    return depthmix_launch<__nv_bfloat16>(cp, n_cands, w, out_h, out_rn, inv_out, out_index, uses_cache, rows, C, st);
   set_error("depthmix: unknown dtype %d", dtype);
   return DGPT_E_UNSUPPORTED;
+}
+
+int dgpt_depthmix(const void* const* cands, int32_t n_cands, const void* w, void* out_h, void* out_rn,
+                  int64_t rows, int32_t C, int32_t dtype, void* stream) {
+  return dgpt_depthmix_cached(cands, nullptr, n_cands, w, out_h, out_rn, nullptr, -1, rows, C, dtype, stream);
 }
 
 int dgpt_swiglu(const void* in, void* out, int64_t rows, int32_t n_out, float alpha, float limit, int32_t dtype,

@@ -104,6 +104,7 @@ class Block(nn.Module):
         self.mlp_res_proj = nn.Linear(n_embd, 1, bias=False)
 
 
+CACHE_NORMS = True  # depth mix: reuse the norm factors of committed candidates instead of recomputing them
 FUSED_FFN = True  # first feed-forward GEMM on the library's tcgen05 kernel with the SwiGLU fused (bf16 only)
 FUSED_FFN_MIN_ROWS = 256
 # Cap on the CTAs of the shared-prompt attention phase while it runs beside the per-row phase: None = one per SM
@@ -174,6 +175,9 @@ class ForwardPlan:
         # tcgen05 GEMM + SwiGLU epilogue: bf16 with tileable sizes, and enough rows to fill the tensor cores
         self.fused_ffn = FUSED_FFN and dt == torch.bfloat16 and C % 8 == 0 and n >= FUSED_FFN_MIN_ROWS
         self.f = None if self.fused_ffn else buf(n, 4 * C)
+        # norm factors of committed depth-mix candidates, carried from mix to mix (16-byte rows needed)
+        self.cache_norms = CACHE_NORMS and (C * emb.element_size()) % 16 == 0
+        self.norm_cache: dict[int, torch.Tensor] = {}
         self.prefix_o = None
         self.prefix_lse = None
         self.part_o = None
@@ -181,6 +185,28 @@ class ForwardPlan:
         self.side = None
         self.prefix_ctas = 0
         self.workspace = None
+
+    def _mix(self, cands: list, partial: torch.Tensor, w: torch.Tensor, known: set) -> None:
+        """Depth mix of the committed candidates and the running block sum into self.u.  A committed candidate no
+        longer changes, so the first mix that sees it writes its per-row norm factor and the later ones read it."""
+        if not self.cache_norms:
+            ops.depthmix(cands + [partial], w, None, self.u)
+            return
+        inv_in, inv_out, out_index = [], None, -1
+        for idx, t in enumerate(cands):
+            key = t.data_ptr()
+            if key in known:
+                inv_in.append(self.norm_cache[key])
+            else:
+                inv_in.append(None)
+                if inv_out is None and not any(c.data_ptr() == key for c in cands[:idx]):
+                    buf = self.norm_cache.get(key)
+                    if buf is None:
+                        buf = self.norm_cache[key] = torch.empty(self.n, dtype=torch.float32, device=t.device)
+                    inv_out, out_index = buf, idx
+        ops.depthmix_cached(cands + [partial], inv_in + [None], w, None, self.u, inv_out, out_index)
+        if inv_out is not None:
+            known.add(cands[out_index].data_ptr())
 
     def _decode_extras(self, b: KvBinding) -> None:
         m = self.model
@@ -212,12 +238,13 @@ class ForwardPlan:
         ops.embed_rmsnorm(ids32, W.emb, self.x)
         cands = [self.x]
         partial = self.x
+        known: set[int] = set()  # committed candidates whose norm factor has been written during this forward
         for i in range(L):
             lw = W.layers[i]
             if i == 0:
                 ops.depthmix([self.x], None, None, self.u)  # single candidate: mix is the identity
             else:
-                ops.depthmix(cands + [partial], lw.w_attn, None, self.u)
+                self._mix(cands, partial, lw.w_attn, known)
             if (i + 1) % m.attn_res_layers_per_block == 0:
                 cands = cands + [partial]
                 partial = None
@@ -271,7 +298,7 @@ class ForwardPlan:
                 else:  # layers_per_block > 1: the running block sum keeps accumulating
                     torch.addmm(partial, self.y, lw.wproj_t, out=part)
             partial = part
-            ops.depthmix(cands + [partial], lw.w_mlp, None, self.u)
+            self._mix(cands, partial, lw.w_mlp, known)
             if self.fused_ffn:  # first FFN GEMM with the SwiGLU in its epilogue (the [n, 4C] product never reaches HBM)
                 ops.linear(self.u, lw.w1, self.act, swiglu=(m.swiglu_alpha, m.swiglu_limit), status=self.status)
             else:

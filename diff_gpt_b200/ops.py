@@ -86,6 +86,36 @@ def depthmix(
     check(lib.dgpt_depthmix(arr, len(cands), _ptr(w), _ptr(out_h), _ptr(out_rn), rows, Cdim, dtype_code(c0), _stream()))
 
 
+def depthmix_cached(
+    cands: list[torch.Tensor],
+    cand_inv: list[torch.Tensor | None],
+    w: torch.Tensor | None,
+    out_h: torch.Tensor | None,
+    out_rn: torch.Tensor | None,
+    inv_out: torch.Tensor | None = None,
+    inv_out_index: int = -1,
+) -> None:
+    """`depthmix` that reads the norm factors in `cand_inv` (fp32 [rows] each, None = compute) and writes the one it
+    computes for candidate `inv_out_index` into `inv_out`."""
+    _cuda(*cands, *[t for t in cand_inv if t is not None], w, out_h, out_rn, inv_out)
+    c0 = cands[0]
+    Cdim = c0.shape[-1]
+    rows = c0.numel() // Cdim
+    assert len(cand_inv) == len(cands)
+    for c in cands:
+        assert c.is_contiguous() and c.shape == c0.shape and c.dtype == c0.dtype
+    for t in [*cand_inv, inv_out]:
+        assert t is None or (t.dtype == torch.float32 and t.numel() == rows and t.is_contiguous())
+    arr = (C.c_void_p * len(cands))(*[c.data_ptr() for c in cands])
+    inv = (C.c_void_p * len(cands))(*[None if t is None else t.data_ptr() for t in cand_inv])
+    check(
+        lib.dgpt_depthmix_cached(
+            arr, inv, len(cands), _ptr(w), _ptr(out_h), _ptr(out_rn), _ptr(inv_out), inv_out_index, rows, Cdim,
+            dtype_code(c0), _stream(),
+        )
+    )
+
+
 def rope_qknorm_kvappend(
     q: torch.Tensor,
     k: torch.Tensor,

@@ -81,6 +81,17 @@ int dgpt_embed_rmsnorm(const int32_t* ids, const void* emb, void* out, int64_t n
 int dgpt_depthmix(const void* const* cands, int32_t n_cands, const void* w, void* out_h, void* out_rn,
                   int64_t rows, int32_t C, int32_t dtype, void* stream);
 
+/* dgpt_depthmix with the candidates' norm factors carried from one mix to the next.  A committed block output
+ * does not change any more, yet every later mix (two per layer) needs rsqrt(mean(cand^2) + eps) of each of its
+ * rows again.  cand_inv: HOST array of n_cands device fp32 [rows] pointers (or NULL entries / NULL array): where
+ * given, the factor is read instead of being recomputed.  inv_out: device fp32 [rows] or NULL: receives the
+ * factor this call computes for candidate inv_out_index (which must not have one passed in).  The factor is the
+ * number the plain call computes, so results do not depend on what is cached.  Needs 16-byte aligned rows of a
+ * multiple of 16 bytes when any factor is passed or requested (DGPT_E_UNSUPPORTED otherwise). */
+int dgpt_depthmix_cached(const void* const* cands, const float* const* cand_inv, int32_t n_cands, const void* w,
+                         void* out_h, void* out_rn, float* inv_out, int32_t inv_out_index, int64_t rows, int32_t C,
+                         int32_t dtype, void* stream);
+
 /* RoPE on q and k, RMSNorm over head_dim on both, then append k and v to the cache.
  *   token (s, t), s < n_seq, t < T:   position = seq_pos0[s] + step + t   (RoPE row)
  *                                     slot     = seq_slot0[s] + step + t  (cache slot)

@@ -73,6 +73,22 @@ def test_depthmix_golden_and_random(dtype, tol, tag):
     assert _rel(o_same, o_copy) <= (1e-6 if dtype == torch.float32 else 8e-3)
     ops.depthmix([base[1], base[1], base[1]], wv, o_one, None)
     assert torch.equal(o_one, base[1])
+    # norm factors carried between mixes: written by one call, read by the next, same bits as without them
+    rows = 37
+    pool = [(torch.randn(rows, 768, generator=gen) * (1 + i)).to(dtype).cuda() for i in range(5)]
+    wv = (torch.randn(768, generator=gen) * 0.2).to(dtype).cuda()
+    plain, first, second = (torch.empty(rows, 768, dtype=dtype, device="cuda") for _ in range(3))
+    lst = [pool[0], pool[0], pool[1], pool[2], pool[3], pool[4]]
+    ops.depthmix(lst, wv, None, plain)
+    inv = [torch.full((rows,), float("nan"), device="cuda") for _ in range(3)]
+    ops.depthmix_cached(lst, [None] * 6, wv, None, first, inv[0], 0)      # writes the factor of pool[0]
+    ops.depthmix_cached(lst, [inv[0], inv[0], None, None, None, None], wv, None, second, inv[1], 2)  # reads it, writes pool[1]'s
+    assert torch.equal(first, plain) and torch.equal(second, plain)
+    want_inv = torch.rsqrt(pool[1].float().pow(2).mean(-1) + 1.1920928955078125e-07)
+    assert torch.isfinite(inv[0]).all() and (inv[1] - want_inv).abs().max().item() <= 1e-6 * want_inv.abs().max().item()
+    third = torch.empty_like(plain)
+    ops.depthmix_cached(lst, [inv[0], inv[0], inv[1], None, None, None], wv, None, third)
+    assert torch.equal(third, plain)
     # candidate counts on both sides of the shared-memory-staged kernel's limit (32), odd row count
     for n_c in (2, 3, 13, 17, 32, 33):
         cs = [(torch.randn(11, 768, generator=gen) * (1 + 0.3 * i)).to(dtype) for i in range(n_c)]
