@@ -74,6 +74,7 @@ PROTOTYPES = {
     "dgpt_step_advance": (C.c_int, [_p, _i32, _p]),
     "dgpt_linear": (C.c_int, [_p, _i64, _p, _i64, _p, _i64, _p, _i64, _i32, _i32, _i32, _i32, _f32, _f32, _i32, _p, _p]),
     "dgpt_integrate_tokens": (C.c_int, [_p, _i64, _i32, _i32, _i32, _i32, _p, _p, _p, _i32, _p, _p]),
+    "dgpt_encode_series": (C.c_int, [_p, _i64, _i32, _i32, _i32, _i32, _p, _i32, _i32, _p, _p, _p, _p, _p]),
     "dgpt_bounded_wait_probe": (C.c_int, [_i32, _i64, _p, _p]),
     "dgpt_token_nll": (C.c_int, [_p, _i64, _p, _p, _i32, _i32, _i32, _p, _p]),
     "dgpt_sample": (

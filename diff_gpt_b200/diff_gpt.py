@@ -100,25 +100,61 @@ class DiffGPT:
             f"context positions, but block_size is {self.model.block_size}"
         )
 
-    def _future_samples_on_device(self, df: pd.DataFrame, max_new_points: int, sampler: Sampler | None, num_samples: int) -> torch.Tensor:
-        """(num_samples, max_new_points, n_features) float64 ON THE DEVICE: tokens are decoded where they were
-        sampled (`dgpt_integrate_tokens`), continuing the cumulative sums from the state the context leaves."""
+    def _encode_on_device(self, values: np.ndarray):
+        """values f64 [S, rows, F] -> (tokens int32 [S, rows - max_k, F], end state f64 [S, F, max(max_k, 1)], scale,
+        orders), all on the model's device: one `dgpt_encode_series` launch tokenises every series and leaves the
+        running sums the decoder continues from."""
         from . import ops
-        from .encoder_decoder import _orders, integrate_end_state
+        from .encoder_decoder import _orders, _scalar, column_scales
 
-        columns = df.shape[1]
-        start, scale, encoded = self._encode(df.to_numpy(dtype=np.float64))
-        prompt = encoded.reshape(-1).astype(np.int64).tolist()  # row-major: (time, channel)
-        generated, _ = self._get_engine().generate_many([prompt], num_samples, max_new_points * columns, sampler)
-        V = self.model.vocab_size
-        scale_cols = np.array(np.broadcast_to(np.asarray(scale, dtype=np.float64).reshape(-1), (columns,)))  # a writable copy
-        state = integrate_end_state(start, (encoded - V // 2) / scale, self.order_of_derivative)
-        dev = generated.device
-        return ops.integrate_tokens(
-            generated[0], columns, V, torch.from_numpy(scale_cols).to(dev),
-            torch.from_numpy(_orders(self.order_of_derivative, columns).astype(np.int32)).to(dev),
-            torch.from_numpy(state).to(dev),
+        assert not self.use_decimal, "the Decimal code path of the reference codec is not part of this build"
+        assert values.dtype == np.float64 and values.ndim == 3
+        columns = values.shape[2]
+        dev = self.model.token_embedding_table.weight.device
+        orders = _orders(self.order_of_derivative, columns)
+        scale = torch.from_numpy(column_scales(self.model.vocab_size, self.domain_of_definition, orders)).to(dev)
+        orders_dev = torch.from_numpy(orders.astype(np.int32)).to(dev)
+        tokens, _start, state = ops.encode_series(
+            torch.tensor(values, dtype=torch.float64).to(dev), self.model.vocab_size, scale, orders_dev,
+            int(orders.max()) if columns else 0, _scalar(self.order_of_derivative),
         )
+        return tokens, state, scale, orders_dev
+
+    def _future_samples_on_device(self, df: pd.DataFrame, max_new_points: int, sampler: Sampler | None, num_samples: int) -> torch.Tensor:
+        """(num_samples, max_new_points, n_features) float64 ON THE DEVICE."""
+        values = df.to_numpy(dtype=np.float64)
+        return self._many_futures_on_device(values[None], max_new_points, sampler, num_samples)[0]
+
+    def _many_futures_on_device(self, values: np.ndarray, max_new_points: int, sampler: Sampler | None, num_samples: int) -> torch.Tensor:
+        """(S, num_samples, max_new_points, n_features) float64 ON THE DEVICE for S equally shaped series: the
+        series are tokenised where the model lives (`dgpt_encode_series`), all prompts are decoded together, and
+        the tokens are turned back into values where they were sampled (`dgpt_integrate_tokens`), continuing the
+        cumulative sums from the state each context leaves."""
+        from . import ops
+
+        S, _rows, columns = values.shape
+        tokens, state, scale, orders_dev = self._encode_on_device(values)
+        prompts = tokens.reshape(S, -1)  # row-major: (time, channel)
+        generated, _ = self._get_engine().generate_many(prompts, num_samples, max_new_points * columns, sampler)
+        V = self.model.vocab_size
+        out = torch.empty((S, num_samples, max_new_points, columns), dtype=torch.float64, device=generated.device)
+        for s in range(S):
+            out[s] = ops.integrate_tokens(generated[s], columns, V, scale, orders_dev, state[s])
+        return out
+
+    @torch.inference_mode()
+    def predict_samples_many(self, dfs, max_new_points: int, num_samples: int, sampler: Sampler | None = None) -> np.ndarray:
+        """`predict_samples` for several equally shaped frames in one decode: (S, num_samples, max_new_points, F).
+        The reference loops over series on the host (benchmarks/prob_m4_bench.py:174-182).  Trajectory n of
+        series s draws the random stream keyed by (s, n); `predict_samples` is the case S = 1."""
+        assert isinstance(self.model, GPT), "predict_samples_many needs the diff_gpt_b200 GPT"
+        assert len(dfs) > 0
+        shape = dfs[0].shape
+        for df in dfs:
+            assert df.shape == shape, "all frames must have the same shape"
+            self._check_future_request(df, max_new_points, num_samples)
+        values = np.stack([df.to_numpy(dtype=np.float64) for df in dfs])
+        return self._many_futures_on_device(values, max_new_points, sampler, num_samples).cpu().numpy()
 
     def _generate_future_samples(self, df: pd.DataFrame, max_new_points: int, sampler: Sampler | None, num_samples: int) -> np.ndarray:
         """(num_samples, max_new_points, n_features) float64: the forecast rows only."""

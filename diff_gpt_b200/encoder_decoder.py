@@ -179,6 +179,17 @@ def _mash(x: np.ndarray, k: int, vocab_size: int) -> np.ndarray:
     return np.clip(tok, 0, vocab_size - 1)
 
 
+def column_scales(vocab_size: int, domain_of_definition: np.ndarray, orders: np.ndarray) -> np.ndarray:
+    """Tokens per unit of the k-th difference, per column: the largest difference lands one token inside the
+    vocabulary's edge, less the 2^k headroom the cascaded quantiser needs (encoder_decoder.py:311-325)."""
+    scale = np.ones(len(orders), dtype=np.float64)
+    for c, k in enumerate(orders):
+        if abs(domain_of_definition[c]) > np.finfo(np.float64).eps:
+            room = vocab_size - 2 - (2 ** int(k) if _uses_mash(int(k), vocab_size) else 0)
+            scale[c] = room / domain_of_definition[c] / 2
+    return scale
+
+
 def encode(inp: np.ndarray, vocab_size: int, domain_of_definition: np.ndarray, order_of_derivative, use_decimal: bool):
     """-> (start, scale, tokens[rows - max_k, F] int64) (encoder_decoder.py:278-370)."""
     _no_decimal(use_decimal)
@@ -187,11 +198,7 @@ def encode(inp: np.ndarray, vocab_size: int, domain_of_definition: np.ndarray, o
     n_cols = inp.shape[1]
     assert domain_of_definition.shape[0] == n_cols
     orders = _orders(order_of_derivative, n_cols)
-    scale = np.ones(n_cols, dtype=np.float64)
-    for c, k in enumerate(orders):
-        if abs(domain_of_definition[c]) > np.finfo(np.float64).eps:
-            room = vocab_size - 2 - (2 ** int(k) if _uses_mash(int(k), vocab_size) else 0)
-            scale[c] = room / domain_of_definition[c] / 2
+    scale = column_scales(vocab_size, domain_of_definition, orders)
     start, diff = differentiate(inp, order_of_derivative)
     scaled = diff * scale
     tokens = np.zeros(scaled.shape, dtype=np.int64)

@@ -310,6 +310,31 @@ def integrate_tokens(
     return out
 
 
+def encode_series(
+    values: torch.Tensor, vocab_size: int, scale: torch.Tensor, order: torch.Tensor, max_order: int, scalar_order: bool
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Tokenise many series at once: f64 [S, rows, F] -> (tokens int32 [S, rows - max_order, F],
+    start f64 [S, max_order, F], end state of the decoder's running sums f64 [S, F, max(max_order, 1)])."""
+    _cuda(values, scale, order)
+    assert values.dtype == torch.float64 and values.dim() == 3 and values[0].is_contiguous()
+    S, rows, F = values.shape
+    assert scale.dtype == torch.float64 and order.dtype == torch.int32
+    assert scale.shape == (F,) and order.shape == (F,) and scale.is_contiguous() and order.is_contiguous()
+    assert 0 <= max_order <= rows
+    dev = values.device
+    tokens = torch.empty((S, rows - max_order, F), dtype=torch.int32, device=dev)
+    start = torch.empty((S, max_order, F), dtype=torch.float64, device=dev)
+    state = torch.empty((S, F, max(max_order, 1)), dtype=torch.float64, device=dev)
+    check(
+        lib.dgpt_encode_series(
+            values.data_ptr(), values.stride(0) if S > 1 else rows * F, S, rows, F, vocab_size, order.data_ptr(),
+            max_order, 1 if scalar_order else 0, scale.data_ptr(), tokens.data_ptr(), start.data_ptr(),
+            state.data_ptr(), _stream(),
+        )
+    )
+    return tokens, start, state
+
+
 def token_nll(logits: torch.Tensor, targets: torch.Tensor, status: torch.Tensor | None = None) -> torch.Tensor:
     """-log softmax(logits)[r, targets[r]] per row as fp32 [R]; logits [R, V] (last dim contiguous), targets int32 [R]."""
     _cuda(logits, targets, status)

@@ -251,6 +251,25 @@ int dgpt_integrate_tokens(const int32_t* tokens, int64_t token_row_stride, int32
                           int32_t n_chan, int32_t vocab_size, const double* scale, const int32_t* order,
                           const double* state, int32_t max_order, double* out, void* stream);
 
+/* Values of many series -> prompt tokens in one launch (one thread per series and channel walks the rows):
+ *   order[channel]-th finite differences, times scale[channel], then the quantiser the reference picks for the
+ *   column: rounding (order 0 among per-column orders), the first-order sigma-delta, or the cascade of
+ *   `order` first-order loops when vocab_size > 2^order + 2.  Every float64 operation is the one numpy
+ *   performs, in its order: tokens and start rows are bit-identical to the host codec's.
+ * Replaces the per-series call of src/diff_gpt/encoder_decoder.py:278-370 (:36-94, :155-226, :229-275).
+ * values: device f64 [n_series, rows, n_chan] with series stride (elements);
+ * order: device int32 [n_chan] (each <= max_order <= 8, max_order = the largest); scalar_order: 1 when the
+ * model was given ONE order for all columns (start rows are then the first value of each difference level,
+ * else the first max_order raw rows); scale: device f64 [n_chan];
+ * tokens: device int32 [n_series, rows - max_order, n_chan];
+ * start: device f64 [n_series, max_order, n_chan] or NULL;
+ * state: device f64 [n_series, n_chan, max(max_order, 1)] or NULL: the running sums the decoder has reached at
+ * the end of the prompt, which dgpt_integrate_tokens continues from. */
+int dgpt_encode_series(const double* values, int64_t series_stride, int32_t n_series, int32_t rows,
+                       int32_t n_chan, int32_t vocab_size, const int32_t* order, int32_t max_order,
+                       int32_t scalar_order, const double* scale, int32_t* tokens, double* start,
+                       double* state, void* stream);
+
 /* *step_ptr += delta, as a one-thread kernel on `stream`: the last node of a captured decode step,
  * so that replaying the same launch sequence walks through the positions.  (The reference keeps the
  * position on the host: src/diff_gpt/model/kv_cache.py:113-115.) */
