@@ -115,7 +115,7 @@ class DiffGPT:
         scale = torch.from_numpy(column_scales(self.model.vocab_size, self.domain_of_definition, orders)).to(dev)
         orders_dev = torch.from_numpy(orders.astype(np.int32)).to(dev)
         tokens, _start, state = ops.encode_series(
-            torch.tensor(values, dtype=torch.float64).to(dev), self.model.vocab_size, scale, orders_dev,
+            torch.from_numpy(np.array(values, dtype=np.float64, order="C")).to(dev), self.model.vocab_size, scale, orders_dev,
             int(orders.max()) if columns else 0, _scalar(self.order_of_derivative),
         )
         return tokens, state, scale, orders_dev
