@@ -273,15 +273,17 @@ class DiffGPT:
         max_order = self._max_order(columns, "columns")
         assert max_order <= T, f"max order {max_order} > signal length {T}"
         inp = df.to_numpy(dtype=np.float64)
-        _, _, encoded = self._encode(inp)
-        N = encoded.size
+        N = (T - max_order) * columns
         assert N <= self.model.block_size, (
             f"signal has {N} tokens but block_size is {self.model.block_size}; "
             f"chunk the input manually for longer sequences"
         )
         device = torch.device(self.model.device_type)
-        flat_tokens = encoded.reshape(-1).astype(np.int64)
-        tokens = torch.as_tensor(flat_tokens, dtype=torch.int64, device=device).unsqueeze(0)  # (1, N)
+        if isinstance(self.model, GPT):  # tokenised where the model lives
+            tokens = self._encode_on_device(inp[None])[0].reshape(1, N).to(torch.int64)
+        else:
+            _, _, encoded = self._encode(inp)
+            tokens = torch.as_tensor(encoded.reshape(-1).astype(np.int64), dtype=torch.int64, device=device).unsqueeze(0)
         was_training = self.model.training
         self.model.eval()
         logits, _ = self.model.forward(tokens)  # (1, N, V); row i predicts token i + 1
@@ -294,7 +296,7 @@ class DiffGPT:
             flat[1:] = nll.cpu().numpy().astype(np.float64)
             assert int(status.item()) == 0, "a token id was outside the vocabulary"
         out = np.full((T, columns), np.nan, dtype=np.float64)
-        out[max_order:] = flat.reshape(encoded.shape[0], columns)
+        out[max_order:] = flat.reshape(T - max_order, columns)
         return pd.DataFrame(out, columns=df.columns, index=df.index)
 
     # ---- checkpoints --------------------------------------------------------------------
