@@ -15,7 +15,9 @@ order-1 sigma-delta encoder; nothing is read from disk.
 
 One JSON line is printed by rank 0.  `value` is device-timed with the prompts
 already resident in HBM; `e2e` goes through `Engine.generate_many` with host
-prompts and a device->host copy of all tokens inside the timed region.  The KV
+prompts and a device->host copy of all tokens inside the timed region, and at N = 1
+`e2e.predict_samples` times the reference's own call, `DiffGPT.predict_samples`, from a
+float64 host frame to the float64 host array of forecasts.  The KV
 pool (38.7 GB per rank) is far larger than L2, so no explicit L2 flush is needed.
 """
 
@@ -64,15 +66,19 @@ def peaks() -> dict:
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def synthetic_series(n_series: int) -> list[np.ndarray]:
+    """Random walk (step sd 0.5) + sin(2 pi t / 24), 1025 points per series, float64 [1025, 1]."""
+    rng = np.random.default_rng(4)
+    t = np.arange(PROMPT_TOKENS + 1)
+    return [(np.cumsum(rng.normal(0.0, 0.5, t.size)) + np.sin(2 * np.pi * t / 24.0)).reshape(-1, 1) for _ in range(n_series)]
+
+
 def synthetic_prompts(n_series: int, vocab: int) -> list[list[int]]:
-    """Random walk (step sd 0.5) + sin(2 pi t / 24), 1025 points -> 1024 order-1 tokens per series."""
+    """The synthetic series as 1024 order-1 tokens each."""
     from diff_gpt_b200.encoder_decoder import encode, get_domain_of_definition
 
-    rng = np.random.default_rng(4)
     out = []
-    t = np.arange(PROMPT_TOKENS + 1)
-    for _ in range(n_series):
-        x = (np.cumsum(rng.normal(0.0, 0.5, t.size)) + np.sin(2 * np.pi * t / 24.0)).reshape(-1, 1)
+    for x in synthetic_series(n_series):
         dom = get_domain_of_definition(x, 1, use_decimal=False)
         _, _, tok = encode(inp=x, vocab_size=vocab, domain_of_definition=dom, order_of_derivative=1, use_decimal=False)
         out.append(tok.reshape(-1).astype(np.int64).tolist())
@@ -345,6 +351,46 @@ def run_ours(args) -> None:
         "d2h_bytes_per_step": series_per_step * TRAJECTORIES * HORIZON * 4,
         "steps": e2e_steps, "api": "Engine.generate_many(host prompts) -> pinned host int32 tokens",
     }
+
+    # ---- the same through the reference's own call: DiffGPT.predict_samples, values in, values out ----
+    # One series of 4096 trajectories per step (the tokens of a 1-GPU step above; measured on one GPU only): a
+    # float64 frame goes in from the host, is tokenised on the device, decoded, turned back into values and
+    # comes back as a float64 host array.
+    if e2e is not None and world == 1:
+        try:
+            import pandas as pd
+
+            from diff_gpt_b200.diff_gpt import DiffGPT
+            from diff_gpt_b200.encoder_decoder import get_domain_of_definition
+
+            engine.release()
+            series = synthetic_series(N_SERIES)
+            doms = [get_domain_of_definition(x, 1, use_decimal=False) for x in series]
+            frames = [pd.DataFrame(x, columns=["y"]) for x in series]
+            dg = DiffGPT(model=model, order_of_derivative=1, domain_of_definition=doms[0], use_decimal=False)
+
+            def api_step(i: int) -> np.ndarray:
+                sidx = (i * world + rank) % N_SERIES
+                dg.domain_of_definition = doms[sidx]
+                return dg.predict_samples(frames[sidx], max_new_points=HORIZON, num_samples=TRAJECTORIES, sampler=sampler)
+
+            fut = api_step(0)
+            assert fut.shape == (TRAJECTORIES, HORIZON, 1) and np.isfinite(fut).all()
+            barrier()
+            t0 = time.perf_counter()
+            for i in range(e2e_steps):
+                api_step(1 + i)
+            barrier()
+            api_s = time.perf_counter() - t0
+            e2e["predict_samples"] = {
+                "value": e2e_steps * world * TRAJECTORIES * HORIZON / api_s, "unit": "tokens/s",
+                "h2d_bytes_per_step": world * (PROMPT_TOKENS + 1) * 8, "d2h_bytes_per_step": world * TRAJECTORIES * HORIZON * 8,
+                "api": "DiffGPT.predict_samples(host float64 frame) -> host float64 [4096, 256, 1], one series per step",
+            }
+            dg._get_engine().release()
+            del dg
+        except Exception as exc:  # the headline figures above do not depend on this leg
+            e2e["predict_samples"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
     # ---- per-kernel device time: one more step, launched eagerly with events around every call ----
     roof, kernels = None, None
