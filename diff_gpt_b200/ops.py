@@ -316,8 +316,9 @@ def encode_series(
     """Tokenise many series at once: f64 [S, rows, F] -> (tokens int32 [S, rows - max_order, F],
     start f64 [S, max_order, F], end state of the decoder's running sums f64 [S, F, max(max_order, 1)])."""
     _cuda(values, scale, order)
-    assert values.dtype == torch.float64 and values.dim() == 3 and values[0].is_contiguous()
+    assert values.dtype == torch.float64 and values.dim() == 3
     S, rows, F = values.shape
+    assert S == 0 or values[0].is_contiguous()
     assert scale.dtype == torch.float64 and order.dtype == torch.int32
     assert scale.shape == (F,) and order.shape == (F,) and scale.is_contiguous() and order.is_contiguous()
     assert 0 <= max_order <= rows
@@ -325,6 +326,8 @@ def encode_series(
     tokens = torch.empty((S, rows - max_order, F), dtype=torch.int32, device=dev)
     start = torch.empty((S, max_order, F), dtype=torch.float64, device=dev)
     state = torch.empty((S, F, max(max_order, 1)), dtype=torch.float64, device=dev)
+    if S == 0:
+        return tokens, start, state
     check(
         lib.dgpt_encode_series(
             values.data_ptr(), values.stride(0) if S > 1 else rows * F, S, rows, F, vocab_size, order.data_ptr(),
