@@ -170,6 +170,7 @@ struct KvView {
   const int* page_table;
   int page_tokens;
   int max_pages;
+  long long n_pages;  // pages addressable through the table (0 = not stated)
 };
 
 inline KvView make_view(const dgpt_kv_layout* l) {
@@ -181,6 +182,7 @@ inline KvView make_view(const dgpt_kv_layout* l) {
   w.page_table = l->page_table;
   w.page_tokens = l->page_tokens;
   w.max_pages = l->max_pages;
+  w.n_pages = l->page_table ? l->n_pages : 0;
   return w;
 }
 

@@ -7,6 +7,8 @@
 // softmax state; the groups are merged with shuffles at the end, so the inner
 // loop has no cross-group dependency.  HBM-bound by design: the algorithmic
 // traffic is 2 * D * sizeof(T) bytes per (row, head, key).
+#include <atomic>
+
 #include "common.cuh"
 
 namespace dgpt {
@@ -35,12 +37,8 @@ __device__ __forceinline__ void merge_partial(float& m, float& l, float* acc, fl
   m = mn;
 }
 
-#ifndef DGPT_DEC_U
-#define DGPT_DEC_U 8        // 16-byte loads in flight per lane and per tensor
-#endif
-#ifndef DGPT_DEC_MINB
-#define DGPT_DEC_MINB 4     // minimum resident CTAs per SM asked of the compiler
-#endif
+constexpr int kDecLoads = 8;    // 16-byte loads in flight per lane and per tensor
+constexpr int kDecMinCtas = 4;  // minimum resident CTAs per SM asked of the compiler
 
 // U = 16-byte loads in flight per lane and tensor, MINB = resident CTAs per SM asked of the compiler.  (8, 4) is the
 // fastest form of the kernel by itself (99 % of the copy bandwidth); (4, 8) needs half the registers per CTA and is
@@ -65,9 +63,12 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
   const int split = blockIdx.y;
   const int step = step_ptr ? *step_ptr : 0;
   const bool have_prefix = prefix_lse != nullptr;
-  const int n0 = (have_prefix || len0 == nullptr) ? 0 : len0[r];
-  const int s1 = start1[r];
-  const int n = n0 + len1[r] + step;
+  // A range that would run past the sequence's slots is cut at the capacity (the append kernel reports such a
+  // step through its status word); nothing outside the page table or the pool is ever read.
+  const int cap = kv.page_table ? kv.max_pages * kv.page_tokens : kv.page_tokens;
+  const int n0 = min(max((have_prefix || len0 == nullptr) ? 0 : len0[r], 0), cap);
+  const int s1 = min(max(start1[r], 0), cap);
+  const int n = n0 + min(max(len1[r] + step, 0), cap - s1);
   int chunk = (n + n_splits - 1) / n_splits;
   chunk = (chunk + 2 * TPW - 1) / (2 * TPW) * (2 * TPW);
   const int begin = split * chunk;
@@ -92,7 +93,11 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
     const int lp = slot / kv.page_tokens;
     const int in = slot - lp * kv.page_tokens;
     const int cnt = min((in0 ? min(n0, end) : end) - i, kv.page_tokens - in);
-    const long long pg = kv.page_table ? (long long)kv.page_table[(long long)r * kv.max_pages + lp] : (long long)r;
+    long long pg = kv.page_table ? (long long)kv.page_table[(long long)r * kv.max_pages + lp] : (long long)r;
+    if (kv.n_pages > 0 && (pg < 0 || pg >= kv.n_pages)) {  // a table entry outside the pool: skip its keys
+      i += cnt;
+      continue;
+    }
     const long long base = pg * kv.page_stride + (long long)h * kv.head_stride + (long long)in * D + e * VEC;
     for (int t0 = 0; t0 < cnt; t0 += U * TPW) {
       uint4 kr[U], vr[U];
@@ -157,7 +162,7 @@ decode_attn_kernel(const T* __restrict__ q, long long q_stride, KvView kv, const
   }
   if (g != 0) return;
 
-  if (n_splits > 1) {
+  if (n_splits > 1) {  // ws_o comes first in the workspace, so every 16-byte store below is aligned
     const long long slot = (long long)split * R * H + rh;
     if (e == 0) {
       ws_ml[2 * slot] = m;
@@ -291,16 +296,18 @@ static int decode_launch(const void* q, long long q_stride, const KvView& kv, co
                          int n_splits, int R, int H, cudaStream_t st, float* part_o = nullptr,
                          float* part_lse = nullptr) {
   const long long RH = (long long)R * H;
-  float* ws_ml = ws;
-  float* ws_o = ws ? ws + 2 * RH * n_splits : nullptr;
+  // Workspace = [n_splits][R*H][D] accumulators, then [n_splits][R*H][2] (max, sum).  The accumulators are written
+  // with 16-byte stores and D is a multiple of 4 floats, so with the block first they are aligned for every R*H*n_splits.
+  float* ws_o = ws;
+  float* ws_ml = ws ? ws + RH * n_splits * D : nullptr;
   const float scale_log2 = kLog2e / sqrtf((float)D);
   dim3 grid((unsigned)((RH + 3) / 4), (unsigned)n_splits);
   if (part_lse)  // runs beside the shared-prompt kernel: the lighter form
-    launch_dep(decode_attn_kernel<T, D, DGPT_DEC_U / 2, DGPT_DEC_MINB * 2>, grid, dim3(128), 0, st, static_cast<const T*>(q),
+    launch_dep(decode_attn_kernel<T, D, kDecLoads / 2, kDecMinCtas * 2>, grid, dim3(128), 0, st, static_cast<const T*>(q),
                q_stride, kv, len0, start1, len1, step_ptr, prefix_o, prefix_lse, static_cast<const T*>(gate), gate_stride,
                static_cast<T*>(y), y_stride, ws_ml, ws_o, part_o, part_lse, n_splits, R, H, scale_log2);
   else
-    launch_dep(decode_attn_kernel<T, D, DGPT_DEC_U, DGPT_DEC_MINB>, grid, dim3(128), 0, st, static_cast<const T*>(q),
+    launch_dep(decode_attn_kernel<T, D, kDecLoads, kDecMinCtas>, grid, dim3(128), 0, st, static_cast<const T*>(q),
                q_stride, kv, len0, start1, len1, step_ptr, prefix_o, prefix_lse, static_cast<const T*>(gate), gate_stride,
                static_cast<T*>(y), y_stride, ws_ml, ws_o, part_o, part_lse, n_splits, R, H, scale_log2);
   if (int e = launch_status("decode_attn")) return e;
@@ -320,7 +327,8 @@ using namespace dgpt;
 
 extern "C" size_t dgpt_decode_attn_workspace_bytes(int32_t R, int32_t H, int32_t D, int32_t n_splits) {
   if (n_splits <= 1) return 0;
-  return (size_t)R * H * n_splits * (size_t)(D + 2) * sizeof(float);
+  const size_t bytes = (size_t)R * H * n_splits * (size_t)(D + 2) * sizeof(float);
+  return (bytes + 15) & ~(size_t)15;
 }
 
 extern "C" int dgpt_decode_attn(const void* q, int64_t q_row_stride, const dgpt_kv_layout* kv, const int32_t* len0,
@@ -341,6 +349,8 @@ extern "C" int dgpt_decode_attn(const void* q, int64_t q_row_stride, const dgpt_
     set_error("decode_attn: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
     return DGPT_E_WORKSPACE;
   }
+  DGPT_REQUIRE(need == 0 || (reinterpret_cast<uintptr_t>(workspace) & 15) == 0,
+               "decode_attn: the workspace must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const KvView view = make_view(kv);
   float* ws = static_cast<float*>(workspace);
@@ -446,7 +456,9 @@ constexpr size_t kStaticScratchFloats = (size_t)4 << 20;  // 16 MiB
 static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
 
 constexpr int kMaxDevices = 64;
-static float* g_scratch_addr[kMaxDevices];  // device address of the array, per device, filled on first use
+// Device address of the array, per device, filled on first use.  Host threads may race to fill an entry; they all
+// store the same value.  The addresses belong to this process's contexts: after cudaDeviceReset they are stale.
+static std::atomic<float*> g_scratch_addr[kMaxDevices];
 
 // Host code sees `g_decode_scratch` only as a stand-in for the symbol; the address a kernel can use has
 // to be asked for, with the device that will run the kernel current.
@@ -457,16 +469,18 @@ static int scratch_for_current_device(float** out) {
     set_error("decode_attn_static: cannot identify the current device (%s)", cudaGetErrorString(e));
     return DGPT_E_CUDA;
   }
-  if (g_scratch_addr[dev] == nullptr) {
+  float* known = g_scratch_addr[dev].load(std::memory_order_acquire);
+  if (known == nullptr) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_decode_scratch);
     if (e != cudaSuccess || p == nullptr) {
       set_error("decode_attn_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
       return DGPT_E_CUDA;
     }
-    g_scratch_addr[dev] = static_cast<float*>(p);
+    known = static_cast<float*>(p);
+    g_scratch_addr[dev].store(known, std::memory_order_release);
   }
-  *out = g_scratch_addr[dev];
+  *out = known;
   return DGPT_OK;
 }
 }  // namespace dgpt

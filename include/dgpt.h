@@ -131,7 +131,8 @@ int dgpt_fmha_prefill(const void* q, int64_t q_batch_stride, int64_t q_row_strid
                       int32_t B, int32_t H, int32_t Tq, int32_t D, int32_t q_offset, int32_t causal,
                       int32_t dtype, int32_t impl, int32_t max_ctas, int32_t* status, void* stream);
 
-/* Bytes of workspace dgpt_decode_attn needs for R rows, H heads, head_dim D and n_splits. */
+/* Bytes of workspace dgpt_decode_attn needs for R rows, H heads, head_dim D and n_splits (a multiple of 16;
+ * the workspace pointer itself must be 16-byte aligned). */
 size_t dgpt_decode_attn_workspace_bytes(int32_t R, int32_t H, int32_t D, int32_t n_splits);
 
 /* Decode attention for one new token per row (Tq = 1), split along the keys.
@@ -179,7 +180,8 @@ int dgpt_attn_merge(const float* o_a, const float* lse_a, const float* o_b, cons
  *   - R * H * n_splits * (D + 2) * 4 bytes must fit in dgpt_decode_attn_static_capacity_bytes()
  *     (16 MiB); larger requests return DGPT_E_WORKSPACE with the numbers in dgpt_last_error.
  *   - The first call on each device looks up the array's device address (with that device current);
- *     make that first call before starting any stream capture.
+ *     make that first call before starting any stream capture.  The address is kept per process and per
+ *     device; it is not valid across cudaDeviceReset (do not reset a device between calls).
  *   - All calls share the one array and it keeps the previous call's contents.  Nothing in it has to
  *     start at zero: every (split, row, head) slot is rewritten by the first pass before the combine
  *     pass reads it.  Two calls that overlap on the GPU (different streams, or graphs replayed

@@ -295,9 +295,94 @@ def anomaly(ref):
     )
 
 
+def _seeded_state_dict(V, C, L, seed, std, dtype):
+    """The weights `oracle.ref_math.random_weights` draws: one torch.Generator(seed), tensors in a fixed order.
+    A test regenerates them from the seed, so a fixture made from these needs to store no weights."""
+    g = torch.Generator().manual_seed(seed)
+
+    def n(*s):
+        return (torch.randn(*s, generator=g) * std).to(dtype)
+
+    w = {"token_embedding_table.weight": n(V, C)}
+    for i in range(L):
+        p = f"blocks.{i}."
+        for name in ("c_q", "c_k", "c_v", "c_g", "c_proj"):
+            w[p + f"sa.{name}.weight"] = n(C, C)
+        w[p + "ffwd.net.0.weight"] = n(4 * C, C)
+        w[p + "ffwd.net.2.weight"] = n(C, 2 * C)
+        w[p + "attn_res_proj.weight"] = n(1, C)
+        w[p + "mlp_res_proj.weight"] = n(1, C)
+    w["lm_head.weight"] = w["token_embedding_table.weight"]
+    return w
+
+
+def _forced_logits(m, prompt, G):
+    """Per-step logits of the reference Engine under its own argmax stream (one trajectory)."""
+    from diff_gpt.model.engine import Engine
+
+    cap = _Capture()
+    res, _ = Engine(m).generate_batch(prompt, num_samples=1, max_tokens=G, sampler=cap)
+    stream = np.asarray(res[0][len(prompt) :], dtype=np.int64)
+    return stream, torch.stack([s[0] for s in cap.seen]).numpy()
+
+
+def cfg4_bf16_init002(ref):
+    """BASELINE config 4 at full architecture (V4096 C768 H12 L12 block 2048), weights N(0, 0.02) seed 4 rounded to
+    bf16, a 300-token seeded prompt, 6 argmax steps: per-step logits of the reference in bf16 and, on the same
+    (bf16-valued) weights, in fp32.  Weights are not stored: they are regenerated from the seed."""
+    from diff_gpt.model.gpt import GPT
+
+    V, C, H, L, block = 4096, 768, 12, 12, 2048
+    sd = _seeded_state_dict(V, C, L, 4, 0.02, torch.bfloat16)
+    prompt = torch.randint(0, V, (300,), generator=torch.Generator().manual_seed(44)).tolist()
+    G = 6
+    out = {}
+    m = GPT(vocab_size=V, n_embd=C, block_size=block, n_head=H, n_layer=L).eval()
+    m.load_state_dict({k: v.float() for k, v in sd.items()})
+    out["stream"], out["logits_bf16"] = _forced_logits(m.to(torch.bfloat16), prompt, G)
+    # fp32 on the same (bf16-valued) weights and the same token stream: one causal forward over prompt + stream
+    m32 = GPT(vocab_size=V, n_embd=C, block_size=block, n_head=H, n_layer=L).eval()
+    m32.load_state_dict({k: v.float() for k, v in sd.items()})
+    ids = torch.tensor([prompt + out["stream"].tolist()[:-1]])
+    with torch.inference_mode():
+        full, _ = m32(ids)
+    out["logits_fp32"] = _np(full[0, len(prompt) - 1 :])
+    np.savez_compressed(
+        os.path.join(HERE, "cfg4_bf16_init002.npz"),
+        meta=np.array([V, C, H, L, block, 4, G], dtype=np.int64),
+        prompt=np.asarray(prompt, dtype=np.int64), stream=out["stream"],
+        logits_bf16=out["logits_bf16"], logits_fp32=out["logits_fp32"],
+    )
+    d = np.abs(out["logits_bf16"] - out["logits_fp32"]).max() / np.abs(out["logits_fp32"]).max()
+    print("cfg4_bf16_init002: reference bf16 vs fp32 rel err", d, "max|logit|", np.abs(out["logits_fp32"]).max())
+
+
+def bf16_wide_init(ref):
+    """A small bf16 model with N(0, 0.15) weights: the reference's logits in bf16 and in fp32 on the same weights.
+    On such weights the reference's own bf16 arithmetic strays furthest from exact arithmetic."""
+    from diff_gpt.model.gpt import GPT
+
+    V, C, H, L, block, B, T = 128, 128, 2, 2, 32, 2, 13
+    sd = _seeded_state_dict(V, C, L, 6, 0.15, torch.bfloat16)
+    idx = torch.randint(0, V, (B, T), generator=torch.Generator().manual_seed(106))
+    out = {}
+    for tag, dt in (("bf16", torch.bfloat16), ("fp32", torch.float32)):
+        m = GPT(vocab_size=V, n_embd=C, block_size=block, n_head=H, n_layer=L).eval()
+        m.load_state_dict({k: v.float() for k, v in sd.items()})
+        m = m.to(dt)
+        with torch.inference_mode():
+            out[tag] = _np(m(idx)[0])
+    np.savez_compressed(
+        os.path.join(HERE, "bf16_wide_init.npz"),
+        meta=np.array([V, C, H, L, block, 6], dtype=np.int64), idx=_np(idx),
+        logits_bf16=out["bf16"], logits_fp32=out["fp32"],
+    )
+    print("bf16_wide_init: reference bf16 vs fp32 rel err", np.abs(out["bf16"] - out["fp32"]).max() / np.abs(out["fp32"]).max())
+
+
 def main():
-    if len(sys.argv) != 2:
-        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference [fixture ...]")
     ref = sys.argv[1]
     sys.path.insert(0, os.path.join(ref, "src"))
     sys.dont_write_bytecode = True
@@ -305,16 +390,20 @@ def main():
     from diff_gpt.model.gpt import GPT
     from diff_gpt.model.kv_cache import KVCache
 
-    small_forward(GPT, KVCache, "small_fp32", torch.float32, 64, 32, 4, 3, 16, 0.3, 0, 2, 9)
-    small_forward(GPT, KVCache, "small_bf16_d64", torch.bfloat16, 128, 128, 2, 2, 32, 0.08, 1, 2, 13)
-    small_forward(GPT, KVCache, "small_bf16_d32", torch.bfloat16, 64, 64, 2, 3, 24, 0.1, 2, 3, 11)
-    config1(ref)
-    samplers(ref)
-    ops(ref)
-    engine_force(ref)
-    codec(ref)
-    teacher_forced(ref)
-    anomaly(ref)
+    only = set(sys.argv[2:])  # no names: every fixture
+
+    def want(name: str) -> bool:
+        return not only or name in only
+
+    if want("small_fp32"):
+        small_forward(GPT, KVCache, "small_fp32", torch.float32, 64, 32, 4, 3, 16, 0.3, 0, 2, 9)
+    if want("small_bf16_d64"):
+        small_forward(GPT, KVCache, "small_bf16_d64", torch.bfloat16, 128, 128, 2, 2, 32, 0.08, 1, 2, 13)
+    if want("small_bf16_d32"):
+        small_forward(GPT, KVCache, "small_bf16_d32", torch.bfloat16, 64, 64, 2, 3, 24, 0.1, 2, 3, 11)
+    for fn in (config1, samplers, ops, engine_force, codec, teacher_forced, anomaly, cfg4_bf16_init002, bf16_wide_init):
+        if want(fn.__name__):
+            fn(ref)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,145 @@
+"""The bf16 composition that the benchmark runs, under the oracle and under reference-made fixtures.
+
+Every model here has head_dim 64 and is decoded with enough rows that the tensor-core kernels are the ones that
+run: the tcgen05 attention for the prompt (prefill and the shared-prompt phase of decode), the per-row attention
+partial + merge, and the tcgen05 feed-forward GEMM with the SwiGLU epilogue (256 rows and up).  Comparisons are
+per-step logits under teacher forcing (the forced stream is the oracle's or the reference's own argmax stream), so
+one near-tie cannot send the two sides down different token paths.  Tolerance for bf16: 2e-2 of max |logit|.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import workloads
+from conftest import load_golden
+from oracle import ref_decode, ref_math
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL = 2e-2
+
+
+def _capped(raw: torch.Tensor, cap: float = 15.0) -> torch.Tensor:
+    return cap * torch.tanh(raw.float() / cap)
+
+
+def _forced_step_logits(model, prompts, n_traj, streams, **kw):
+    """Per-step soft-capped logits [G, S * n_traj, V] of a DecodeRun driven by `streams` (one per series)."""
+    from diff_gpt_b200 import TemperatureSampler
+    from diff_gpt_b200.model.engine import DecodeRun
+
+    G = len(streams[0])
+    run = DecodeRun(model, prompts, n_traj, G, TemperatureSampler(0.0), 42, [list(s) for s in streams], **kw)
+    run.start()
+    got = [_capped(run.logits0).repeat_interleave(n_traj, 0).cpu()]
+    for _ in range(G - 1):
+        run.advance(1)
+        got.append(_capped(run.plan.logits).cpu())
+    run.check_status()
+    hist = run.history.cpu()[:, :G]
+    for s, stream in enumerate(streams):
+        assert hist[s * n_traj : (s + 1) * n_traj].tolist() == [list(stream)] * n_traj
+    return torch.stack(got), run
+
+
+def test_two_series_of_128_trajectories_ragged_prompt_graph_and_overlap():
+    """2 series x 128 trajectories = 256 rows, prompt of 203 tokens (not a multiple of the 64-token page), step graph
+    and two-stream attention on: per-step logits of every row against the oracle's Monte-Carlo decode
+    (reference engine.py:88-154) run on the same forced stream."""
+    shape = ref_math.Shape(vocab_size=256, n_embd=128, n_head=2, n_layer=2, block_size=512)
+    w = ref_math.random_weights(shape, seed=21, dtype=torch.bfloat16, std=0.08)
+    gen = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(0, 256, (203,), generator=gen).tolist() for _ in range(2)]
+    G, N = 7, 128
+    streams, want = [], []
+    for p in prompts:
+        toks, _, logits = ref_decode.mc_decode(shape, w, p, 1, G, temperature=0.0, keep_logits=True)
+        streams.append(toks[0].tolist())
+        want.append(logits[:, 0])  # [G, V]
+    model = workloads.gpu_model(dict(vocab_size=256, n_embd=128, n_head=2, n_layer=2, block_size=512), w, torch.bfloat16)
+    got, run = _forced_step_logits(model, prompts, N, streams, use_graph=True, overlap_prefix=True)
+    assert run.graph is not None and run.plan.fused_ffn and run.plan.side is not None
+    for s in range(2):
+        ref = want[s][:, None, :]
+        err = (got[:, s * N : (s + 1) * N] - ref).abs().max().item() / ref.abs().max().item()
+        assert err <= BF16_TOL, (s, err)
+
+
+def test_config4_architecture_at_its_own_init_against_the_reference():
+    """Config 4's model (V4096 C768 H12 L12, bf16) with its N(0, 0.02) seed-4 weights: 256 trajectories of one series,
+    300-token prompt, forced with the reference's own argmax stream; per-step logits against the reference's bf16
+    logits (fixture made by tests/golden/make_golden.py from the unmodified reference), and closer to the reference's
+    fp32 logits on the same weights than the tolerance as well."""
+    g = load_golden("cfg4_bf16_init002")
+    w = workloads.weights(workloads.CFG4, seed=int(g["meta"][5]), dtype=torch.bfloat16)
+    model = workloads.gpu_model(workloads.CFG4, w, torch.bfloat16)
+    got, run = _forced_step_logits(model, [g["prompt"].tolist()], 256, [g["stream"].tolist()])
+    assert run.plan.fused_ffn and run.plan.side is not None
+    ref16, ref32 = torch.from_numpy(g["logits_bf16"]), torch.from_numpy(g["logits_fp32"])
+    scale = ref32.abs().max().item()
+    err16 = (got - ref16[:, None, :]).abs().max().item() / scale
+    err32 = (got - ref32[:, None, :]).abs().max().item() / scale
+    assert err16 <= BF16_TOL and err32 <= BF16_TOL, (err16, err32)
+    assert bool((got == got[:, :1]).all())  # 256 rows fed the same tokens give the same logits, bit for bit
+
+
+def test_wide_init_kernels_sit_no_further_from_exact_arithmetic_than_the_reference_does():
+    """Weights N(0, 0.15): the reference's bf16 forward rounds the depth-mix weights and products to bf16 and strays
+    about 2 % of max |logit| from its own fp32 result; the kernels accumulate in fp32 and round once, so their
+    distance to the fp32 logits must not exceed the reference's."""
+    g = load_golden("bf16_wide_init")
+    V, C, H, L, block, seed = (int(x) for x in g["meta"])
+    cfg = dict(vocab_size=V, n_embd=C, n_head=H, n_layer=L, block_size=block)
+    w = workloads.weights(cfg, seed=seed, dtype=torch.bfloat16, std=0.15)
+    got = workloads.gpu_model(cfg, w, torch.bfloat16)(torch.from_numpy(g["idx"]).cuda())[0].float().cpu().numpy()
+    scale = np.abs(g["logits_fp32"]).max()
+    ref_err = np.abs(g["logits_bf16"] - g["logits_fp32"]).max() / scale
+    our_err = np.abs(got - g["logits_fp32"]).max() / scale
+    assert our_err <= ref_err, (our_err, ref_err)
+    assert our_err <= BF16_TOL
+
+
+def test_config3_architecture_many_series_one_trajectory_split_keys():
+    """Config 3's model (V1024 C512 H8 of 64, L6, bf16, N(0, 0.02) seed 3), 7-channel frames tokenised with the
+    config's per-column orders, 3 series x 1 trajectory: no prompt sharing, so the per-row kernel reads the whole
+    1106-token cache split along the keys.  Per-step logits under the oracle's argmax stream."""
+    from diff_gpt_b200.model.engine import _pick_splits
+
+    shape = ref_math.Shape(**workloads.CFG3)
+    w = workloads.weights(workloads.CFG3, seed=3, dtype=torch.bfloat16)
+    prompts = [workloads.cfg3_tokens(f) for f in workloads.cfg3_frames(3, 160)]
+    assert len(prompts[0]) == 1106
+    G = 14  # two rows of 7 channels
+    assert _pick_splits(3 * 8, 1106 + G) > 1
+    streams, want = [], []
+    for p in prompts:
+        toks, _, logits = ref_decode.mc_decode(shape, w, p, 1, G, temperature=0.0, keep_logits=True)
+        streams.append(toks[0].tolist())
+        want.append(logits[:, 0])
+    model = workloads.gpu_model(workloads.CFG3, w, torch.bfloat16)
+    got, run = _forced_step_logits(model, prompts, 1, streams)
+    assert run.bind.n_splits > 1 and run.bind.shared_layouts is None
+    for s in range(3):
+        err = (got[:, s] - want[s]).abs().max().item() / want[s].abs().max().item()
+        assert err <= BF16_TOL, (s, err)
+
+
+def test_odd_head_count_single_row_decode_with_split_keys():
+    """n_head = 3 (legal: reference mha.py:18-20), batch 1, 800 cached keys: GPT.forward picks 3 key splits, so the
+    split workspace holds an odd number of (split, row, head) slots.  Logits of the decode step against the oracle's
+    causal forward over the 801 tokens (reference mha.py:65-68 against :61-64)."""
+    from diff_gpt_b200 import KVCache
+    from diff_gpt_b200.model.gpt import _pick_splits
+
+    cfg = dict(vocab_size=64, n_embd=96, n_head=3, n_layer=2, block_size=512)
+    shape = ref_math.Shape(**cfg)
+    w = ref_math.random_weights(shape, seed=8, dtype=torch.float32, std=0.3)
+    idx = torch.randint(0, 64, (1, 801), generator=torch.Generator().manual_seed(8))
+    assert _pick_splits(1 * 3, 801) == 3
+    want = ref_math.forward(shape, w, idx)[:, -1]
+    m = workloads.gpu_model(cfg, w, torch.float32)
+    kv = KVCache(batch_size=1, num_heads=3, seq_len=801, head_dim=32, num_layers=2)
+    m(idx[:, :800].cuda(), kv_cache=kv)
+    got = m(idx[:, 800:].cuda(), kv_cache=kv)[0][:, -1].cpu()
+    assert (got - want).abs().max().item() <= 1e-4 * want.abs().max().item()

@@ -427,3 +427,75 @@ def test_sample_frequencies_follow_softmax():
         freq = torch.bincount(out.cpu().long(), minlength=6).double() / n
         want = torch.softmax(logits[0].double() / T, -1)
         assert (freq - want).abs().max().item() < 0.01, T
+
+
+@pytest.mark.parametrize("dtype,tol,tag", DT)
+@pytest.mark.parametrize("R,H,D,n_splits", [(3, 1, 64, 3), (1, 3, 64, 3), (5, 3, 16, 7), (1, 1, 128, 5)])
+def test_decode_attn_split_with_odd_slot_counts(dtype, tol, tag, R, H, D, n_splits):
+    """Split-K with an odd R*H*n_splits (odd head counts are legal: reference mha.py:18-20 only asks that
+    n_embd % n_head == 0) against the oracle's single-query attention, through a caller workspace and through the
+    library's own scratch array."""
+    ops = _ops()
+    gen = torch.Generator().manual_seed(R * 100 + H * 10 + n_splits)
+    pt = 16
+    lens = [int(x) for x in torch.randint(1, 900, (R,), generator=gen)]
+    lens[0] = 800
+    pages = -(-max(lens) // pt)
+    k = torch.randn(R, H, pages * pt, D, generator=gen).to(dtype)
+    v = torch.randn(R, H, pages * pt, D, generator=gen).to(dtype)
+    pool = torch.full((R * pages + 1, 2, H, pt, D), float("nan"), dtype=dtype)
+    table = torch.randperm(R * pages, generator=gen).to(torch.int32).view(R, pages)
+    for r in range(R):
+        for p in range(pages):
+            pool[table[r, p], 0] = k[r, :, p * pt : (p + 1) * pt]
+            pool[table[r, p], 1] = v[r, :, p * pt : (p + 1) * pt]
+    pool = pool.cuda()
+    lay = ops.kv_layout(pool[0, 0], pool[0, 1], 2 * H * pt * D, pt * D, pt, table.cuda(), n_pages=R * pages)
+    q = torch.randn(R, H * D, generator=gen).to(dtype)
+    gate = torch.randn(R, H * D, generator=gen).to(dtype)
+    zero = torch.zeros(R, dtype=torch.int32, device="cuda")
+    n = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    nbytes = ops.decode_attn_workspace_bytes(R, H, D, n_splits)
+    assert nbytes % 16 == 0
+    ws = torch.empty(nbytes // 4, dtype=torch.float32, device="cuda")
+    y = torch.full((R, H * D), float("nan"), dtype=dtype, device="cuda")
+    ops.decode_attn(q.cuda(), lay, zero, zero, n, None, y, H=H, D=D, gate=gate.cuda(), workspace=ws, n_splits=n_splits)
+    y2 = torch.full_like(y, float("nan"))
+    ops.decode_attn_static(q.cuda(), lay, zero, zero, n, None, y2, H=H, D=D, gate=gate.cuda(), n_splits=n_splits)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2)
+    for r in range(R):
+        qh = q[r].view(1, 1, H, D).transpose(1, 2)
+        att = ref_math.sdpa(qh, k[r : r + 1, :, : lens[r]], v[r : r + 1, :, : lens[r]], q_offset=10**6)
+        want = att.transpose(1, 2).reshape(H * D) * torch.sigmoid(gate[r])
+        assert _rel(y[r], want) <= (2e-5 if dtype == torch.float32 else 1.5e-2), r
+
+
+def test_decode_attn_never_reads_past_the_cache_capacity():
+    """Lengths that run past the page table are cut at the capacity: with NaN in every page the row does not own,
+    the output stays finite and equals attention over the slots that exist."""
+    ops = _ops()
+    R, H, D, pt, pages = 3, 2, 64, 8, 4
+    gen = torch.Generator().manual_seed(11)
+    pool = torch.full((R * pages + 2, 2, H, pt, D), float("nan"), dtype=torch.float32)
+    table = (1 + torch.arange(R * pages, dtype=torch.int32)).view(R, pages)
+    k = torch.randn(R, H, pages * pt, D, generator=gen)
+    v = torch.randn(R, H, pages * pt, D, generator=gen)
+    for r in range(R):
+        for p in range(pages):
+            pool[table[r, p], 0] = k[r, :, p * pt : (p + 1) * pt]
+            pool[table[r, p], 1] = v[r, :, p * pt : (p + 1) * pt]
+    pool = pool.cuda()
+    lay = ops.kv_layout(pool[0, 0], pool[0, 1], 2 * H * pt * D, pt * D, pt, table.cuda(), n_pages=R * pages + 2)
+    q = torch.randn(R, H * D, generator=gen)
+    zero = torch.zeros(R, dtype=torch.int32, device="cuda")
+    n = torch.tensor([pages * pt + 9, pages * pt, 5], dtype=torch.int32, device="cuda")
+    for n_splits in (1, 3):
+        ws = torch.empty(max(ops.decode_attn_workspace_bytes(R, H, D, n_splits) // 4, 4), dtype=torch.float32, device="cuda")
+        y = torch.full((R, H * D), float("nan"), device="cuda")
+        ops.decode_attn(q.cuda(), lay, zero, zero, n, None, y, H=H, D=D, workspace=ws, n_splits=n_splits)
+        assert torch.isfinite(y).all()
+        for r, ln in enumerate([pages * pt, pages * pt, 5]):
+            qh = q[r].view(1, 1, H, D).transpose(1, 2)
+            want = ref_math.sdpa(qh, k[r : r + 1, :, :ln], v[r : r + 1, :, :ln], q_offset=10**6).transpose(1, 2).reshape(-1)
+            assert _rel(y[r], want) <= 2e-5

@@ -40,6 +40,21 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert _lib.lib.dgpt_decode_attn_workspace_bytes(10, 4, 64, 3) == 10 * 4 * 3 * 66 * 4
 
 
+@pytest.mark.parametrize("R,H,D,n_splits", [(3, 1, 64, 3), (1, 3, 64, 3), (5, 3, 8, 7), (1, 1, 16, 3), (7, 5, 128, 9)])
+def test_split_workspace_layout_keeps_16_byte_stores_aligned(R, H, D, n_splits):
+    """The accumulator block [n_splits][R*H][D] leads the workspace and D is a multiple of 4 floats, so every
+    (split, row, head) accumulator starts on a 16-byte boundary whatever the parity of R*H*n_splits; the (max, sum)
+    pairs follow it; the stated size covers both and is itself a multiple of 16."""
+    from diff_gpt_b200 import _lib
+
+    size = _lib.lib.dgpt_decode_attn_workspace_bytes(R, H, D, n_splits)
+    slots = R * H * n_splits
+    assert size % 16 == 0 and size >= slots * (D + 2) * 4
+    for slot in range(slots):
+        assert (slot * D * 4) % 16 == 0
+    assert slots * D * 4 + slots * 2 * 4 <= size
+
+
 def test_cpu_tensors_are_rejected_not_emulated():
     from diff_gpt_b200 import GPT, ops
 
