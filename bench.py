@@ -73,9 +73,24 @@ def synthetic_series(n_series: int) -> list[np.ndarray]:
     return [(np.cumsum(rng.normal(0.0, 0.5, t.size)) + np.sin(2 * np.pi * t / 24.0)).reshape(-1, 1) for _ in range(n_series)]
 
 
+def host_codec():
+    """The host tokeniser (plain numpy), loaded from its file so that a process which only needs prompts (the
+    reference arm) does not import the package and so never maps the CUDA library."""
+    import importlib.util
+
+    name = "_dgpt_host_codec"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, "diff_gpt_b200", "encoder_decoder.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def synthetic_prompts(n_series: int, vocab: int) -> list[list[int]]:
     """The synthetic series as 1024 order-1 tokens each."""
-    from diff_gpt_b200.encoder_decoder import encode, get_domain_of_definition
+    encode, get_domain_of_definition = host_codec().encode, host_codec().get_domain_of_definition
 
     out = []
     for x in synthetic_series(n_series):
@@ -85,16 +100,17 @@ def synthetic_prompts(n_series: int, vocab: int) -> list[list[int]]:
     return out
 
 
-def cfg4_weights(dtype) -> dict:
-    """state_dict of the config-4 model: every parameter ~ N(0, 0.02) from torch.Generator(seed 4)."""
-    g = torch.Generator().manual_seed(WEIGHT_SEED)
-    C, V = CFG4["n_embd"], CFG4["vocab_size"]
+def seeded_weights(cfg: dict, seed: int, dtype, std: float = 0.02) -> dict:
+    """state_dict of a model of shape `cfg`: every parameter ~ N(0, std) from one torch.Generator(seed), drawn in a
+    fixed order (embedding, then per layer q, k, v, g, proj, the two feed-forward matrices, the two depth-mix queries)."""
+    g = torch.Generator().manual_seed(seed)
+    C, V = cfg["n_embd"], cfg["vocab_size"]
 
     def n(*s):
-        return (torch.randn(*s, generator=g) * 0.02).to(dtype)
+        return (torch.randn(*s, generator=g) * std).to(dtype)
 
     w = {"token_embedding_table.weight": n(V, C)}
-    for i in range(CFG4["n_layer"]):
+    for i in range(cfg["n_layer"]):
         p = f"blocks.{i}."
         for name in ("c_q", "c_k", "c_v", "c_g", "c_proj"):
             w[p + f"sa.{name}.weight"] = n(C, C)
@@ -103,6 +119,20 @@ def cfg4_weights(dtype) -> dict:
         w[p + "attn_res_proj.weight"] = n(1, C)
         w[p + "mlp_res_proj.weight"] = n(1, C)
     return w
+
+
+def cfg4_weights(dtype) -> dict:
+    """Config 4: N(0, 0.02), seed 4."""
+    return seeded_weights(CFG4, WEIGHT_SEED, dtype)
+
+
+def load_into(model, w: dict, dtype, device=None):
+    """Weights into a module with the reference's parameter names (the reference's GPT or this package's)."""
+    sd = {k: v.float() for k, v in w.items()}
+    sd["lm_head.weight"] = sd["token_embedding_table.weight"]
+    model.load_state_dict(sd)
+    model = model.to(dtype)
+    return (model.to(device) if device is not None else model).eval()
 
 
 def oracle_shape():
@@ -169,19 +199,79 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------
-# CPU legs (oracle port of the reference path, all host threads)
+# CPU legs: the reference itself when it is installed under baseline/_ref (pip install --target),
+# else the oracle port of the same path; all host threads
 # ---------------------------------------------------------------------------------------
 CPU_SAMPLE = dict(series=1, trajectories=64, steps=32)
 
 
-def cpu_step(shape, w, prompt) -> int:
-    from oracle import ref_decode
+def host_threads() -> int:
+    """Use every core this process may run on (a launcher may have set OMP_NUM_THREADS=1) and say how many."""
+    n = len(os.sched_getaffinity(0))
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
 
-    toks, _, _ = ref_decode.mc_decode(
-        shape, w, prompt, num_samples=CPU_SAMPLE["trajectories"], max_tokens=CPU_SAMPLE["steps"],
-        temperature=TEMPERATURE, top_p=TOP_P, seed=42,
-    )
-    return toks.numel()
+
+class ReferenceSide:
+    """The reference's own classes, imported from baseline/_ref; `available` is False when it is not installed."""
+
+    def __init__(self) -> None:
+        path = os.path.join(ROOT, "baseline", "_ref")
+        self.available = os.path.isdir(os.path.join(path, "diff_gpt"))
+        if not self.available:
+            return
+        if path not in sys.path:
+            sys.path.insert(0, path)
+        from diff_gpt.diff_gpt import DiffGPT
+        from diff_gpt.model.engine import Engine
+        from diff_gpt.model.gpt import GPT
+        from diff_gpt.sampler.nucleus import NucleusSampler
+        from diff_gpt.sampler.temperature import TemperatureSampler
+
+        self.GPT, self.Engine, self.DiffGPT = GPT, Engine, DiffGPT
+        self.NucleusSampler, self.TemperatureSampler = NucleusSampler, TemperatureSampler
+
+    def model(self, cfg: dict, w: dict, dtype, device=None):
+        return load_into(self.GPT(**cfg), w, dtype, device)
+
+
+_REF = None
+
+
+def reference_side() -> ReferenceSide:
+    global _REF
+    if _REF is None:
+        _REF = ReferenceSide()
+    return _REF
+
+
+def cpu_decoder(cfg: dict, w: dict, dtype, top_p, temperature):
+    """decode(prompt, num_samples, max_tokens, force_schedule=None) -> tokens generated, on the host cores, by the
+    reference's Engine.generate_batch (kind "reference") or by the oracle port (kind "port")."""
+    ref = reference_side()
+    if ref.available:
+        model = ref.model(cfg, w, dtype)
+        inner = ref.TemperatureSampler(temperature)
+        sampler = inner if top_p is None else ref.NucleusSampler(top_p, inner)
+
+        def decode(prompt, num_samples, max_tokens, force_schedule=None) -> int:
+            with torch.inference_mode():
+                res, _ = ref.Engine(model).generate_batch(prompt, num_samples=num_samples, max_tokens=max_tokens, sampler=sampler,
+                                                          force_schedule=force_schedule)
+            return sum(len(r) - len(prompt) for r in res)
+
+        return decode, "reference"
+    from oracle import ref_decode, ref_math  # CPU legs only
+
+    shape = ref_math.Shape(**cfg)
+    wd = {k: v.to(dtype) for k, v in w.items()}
+
+    def decode(prompt, num_samples, max_tokens, force_schedule=None) -> int:
+        toks, _, _ = ref_decode.mc_decode(shape, wd, prompt, num_samples=num_samples, max_tokens=max_tokens,
+                                          temperature=temperature, top_p=top_p, seed=42, force_schedule=force_schedule)
+        return toks.numel()
+
+    return decode, "port"
 
 
 def cpu_sample_text() -> str:
@@ -191,28 +281,41 @@ def cpu_sample_text() -> str:
     )
 
 
+def sample_config() -> dict:
+    """What one step of the CPU arm actually runs: the config-4 model and prompt, a bounded number of trajectories and steps."""
+    return {
+        "workload": "BASELINE config 4, bounded sample for the host cores: one series, 64 of its 4096 trajectories, "
+                    "32 of its 256 decode steps, 1024-token prefill included in every step",
+        **CFG4, "prompt_tokens": PROMPT_TOKENS, "horizon": CPU_SAMPLE["steps"], "trajectories_per_series": CPU_SAMPLE["trajectories"],
+        "series_per_step": CPU_SAMPLE["series"], "sampler": f"nucleus p={TOP_P}, temperature {TEMPERATURE}",
+        "sample_of": "BASELINE config 4: large Monte-Carlo decode sharded by trajectory (4096 trajectories x 256 steps per series)",
+        "device": "cpu",
+    }
+
+
 def run_reference(args) -> None:
-    """The reference arm: the CPU port of the reference path on the host cores (rank 0 only)."""
+    """The reference arm: the reference's own code path on the host cores (rank 0 only; other ranks do nothing)."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    shape, w = oracle_shape(), cfg4_weights(torch.bfloat16)
+    cores = host_threads()
+    decode, kind = cpu_decoder(CFG4, cfg4_weights(torch.bfloat16), torch.bfloat16, TOP_P, TEMPERATURE)
     prompt = synthetic_prompts(1, CFG4["vocab_size"])[0]
-    cores = torch.get_num_threads()
     for _ in range(args.warmup):
-        cpu_step(shape, w, prompt)
+        decode(prompt, CPU_SAMPLE["trajectories"], CPU_SAMPLE["steps"])
     t0 = time.perf_counter()
     n = 0
     for _ in range(args.steps):
-        n += cpu_step(shape, w, prompt)
+        n += decode(prompt, CPU_SAMPLE["trajectories"], CPU_SAMPLE["steps"])
     dt = time.perf_counter() - t0
     v = n / dt
     emit({
         "impl": "reference", "metric": "mc_decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": cpu_sample_text()},
+        "config": sample_config(),
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": cpu_sample_text()},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "native_library_loaded": "diff_gpt_b200" in sys.modules,
     })
 
 
