@@ -420,6 +420,14 @@ def run_ours(args) -> None:
     value = args.steps * tokens_per_step / (ms / 1e3)
     assert out.shape == (series_per_step, TRAJECTORIES, HORIZON) and int(out.min()) >= 0 and int(out.max()) < CFG4["vocab_size"]
 
+    # ---- world-size invariance: every N decodes series 0 .. N-1 once more, untimed; the gathered tokens of series 0
+    # (all 4096 trajectories x 256 steps) must be the same bytes whatever N is, so their digest is printed ----
+    import hashlib
+
+    inv_out, _ = device_step(0)
+    invariance = {"series": 0, "shape": list(inv_out[0].shape),
+                  "tokens_sha256": hashlib.sha256(inv_out[0].cpu().numpy().tobytes()).hexdigest()}
+
     # ---- end to end: host prompts in, host tokens out, through the public engine call ----
     # The engine keeps its decode state between calls of one shape, so one untimed call comes first (as the
     # device-timed loop has its warm-up steps); every timed call still uploads its prompts from the host,
@@ -459,6 +467,7 @@ def run_ours(args) -> None:
     # One series of 4096 trajectories per step (the tokens of a 1-GPU step above; measured on one GPU only): a
     # float64 frame goes in from the host, is tokenised on the device, decoded, turned back into values and
     # comes back as a float64 host array.
+    e2e_api = None
     if e2e is not None and world == 1:
         try:
             import pandas as pd
@@ -485,7 +494,7 @@ def run_ours(args) -> None:
                 api_step(1 + i)
             barrier()
             api_s = time.perf_counter() - t0
-            e2e["predict_samples"] = {
+            e2e_api = {
                 "value": e2e_steps * world * TRAJECTORIES * HORIZON / api_s, "unit": "tokens/s",
                 "h2d_bytes_per_step": world * (PROMPT_TOKENS + 1) * 8, "d2h_bytes_per_step": world * TRAJECTORIES * HORIZON * 8,
                 "api": "DiffGPT.predict_samples(host float64 frame) -> host float64 [4096, 256, 1], one series per step",
@@ -493,7 +502,7 @@ def run_ours(args) -> None:
             dg._get_engine().release()
             del dg
         except Exception as exc:  # the headline figures above do not depend on this leg
-            e2e["predict_samples"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+            e2e_api = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
     # ---- per-kernel device time: one more step, launched eagerly with events around every call ----
     roof, kernels = None, None
@@ -508,19 +517,31 @@ def run_ours(args) -> None:
     if world > 1:
         barrier()
 
+    ref_cuda = None
+    if rank == 0 and world == 1 and not args.no_reference_cuda:
+        engine.release()
+        runs.clear()
+        kv_pool = None
+        torch.cuda.empty_cache()
+        ref_cuda = reference_torch_cuda(model, w, prompts[0], dev)
+
     prefill = None if args.no_prefill else prefill_attention(world, rank, dev)
     if world > 1:
         barrier()
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        prompt = prompts[0]
-        shape = oracle_shape()
-        cpu_step(shape, w, prompt)  # warm
+        cores = host_threads()
+        decode, kind = cpu_decoder(CFG4, w, torch.bfloat16, TOP_P, TEMPERATURE)
+        decode(prompts[0], CPU_SAMPLE["trajectories"], 2)  # warm
         t0 = time.perf_counter()
-        n = cpu_step(shape, w, prompt)
+        n = decode(prompts[0], CPU_SAMPLE["trajectories"], CPU_SAMPLE["steps"])
         dt = time.perf_counter() - t0
-        cpu = {"value": n / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": cpu_sample_text()}
+        cpu = {"value": n / dt, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": cpu_sample_text()}
+
+    others = None
+    if rank == 0 and world == 1 and not args.no_other_configs:
+        others = other_configs(dev, cpu=not args.no_cpu)
 
     if rank == 0:
         pk = peaks()
@@ -529,7 +550,8 @@ def run_ours(args) -> None:
             "metric": "mc_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
-            "clocks": clock_info, "e2e": e2e, "gpu_launches": launches, "roofline": roof, "cpu_baseline": cpu,
+            "clocks": clock_info, "e2e": e2e, "e2e_predict_samples": e2e_api, "gpu_launches": launches, "roofline": roof,
+            "cpu_baseline": cpu, "invariance": invariance, "reference_torch_cuda": ref_cuda, "other_configs": others,
             "decode_hbm": {
                 "algorithmic_bytes_per_token": bytes_per_token,
                 "achieved_gbs_per_gpu": value / world * bytes_per_token / 1e9,
@@ -540,6 +562,209 @@ def run_ours(args) -> None:
         emit(line)
     if world > 1:
         dist.destroy_process_group()
+
+
+def _wall(fn, dev, repeat: int = 1) -> float:
+    """Seconds per call of fn(), host clock between two device synchronisations."""
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    for _ in range(repeat):
+        fn()
+    torch.cuda.synchronize(dev)
+    return (time.perf_counter() - t0) / repeat
+
+
+def reference_torch_cuda(model, w: dict, prompt: list[int], dev) -> dict:
+    """The reference's own decode (its Engine, KVCache, samplers and GPT, unmodified, torch kernels) on this GPU in
+    bf16, next to this library through the same call, `Engine.generate_batch(list prompt) -> python lists`, at a
+    trajectory count whose replicated cache fits the reference (it copies the prompt K/V into every row)."""
+    ref = reference_side()
+    if not ref.available:
+        return {"unavailable": "the reference is not installed under baseline/_ref"}
+    from diff_gpt_b200 import Engine, NucleusSampler, TemperatureSampler
+
+    n, horizon = 256, HORIZON
+    out = {"trajectories": n, "horizon": horizon, "prompt_tokens": len(prompt), "unit": "tokens/s",
+           "api": "Engine.generate_batch(python list prompt) -> python lists of tokens and masks"}
+    try:
+        ref_model = ref.model(CFG4, w, torch.bfloat16, dev)
+        ref_sampler = ref.NucleusSampler(TOP_P, ref.TemperatureSampler(TEMPERATURE))
+        with torch.inference_mode():
+            ref.Engine(ref_model).generate_batch(prompt, num_samples=8, max_tokens=4, sampler=ref_sampler)
+            t_ref = _wall(lambda: ref.Engine(ref_model).generate_batch(prompt, num_samples=n, max_tokens=horizon, sampler=ref_sampler), dev)
+        del ref_model
+        torch.cuda.empty_cache()
+        sampler = NucleusSampler(TOP_P, TemperatureSampler(TEMPERATURE))
+        eng = Engine(model)
+        eng.generate_batch(prompt, num_samples=n, max_tokens=horizon, sampler=sampler)
+        t_ours = _wall(lambda: eng.generate_batch(prompt, num_samples=n, max_tokens=horizon, sampler=sampler), dev, repeat=3)
+        eng.release()
+        out.update({"reference_value": n * horizon / t_ref, "reference_s": t_ref, "ours_value": n * horizon / t_ours,
+                    "ours_s": t_ours, "ours_over_reference": t_ref / t_ours})
+    except Exception as exc:  # noqa: BLE001 - the headline figures do not depend on this leg
+        out["error"] = f"{type(exc).__name__}: {exc}"[:300]
+    return out
+
+
+def other_configs(dev, cpu: bool = True) -> dict:
+    """One timed line each for BASELINE configs 1, 2 and 3 on one GPU, with a bounded run of the same call on the host cores."""
+    out = {}
+    for name, fn in (("config1", _config1), ("config2", _config2), ("config3", _config3)):
+        try:
+            out[name] = fn(dev, cpu)
+        except Exception as exc:  # noqa: BLE001 - these lines are additions; the headline does not depend on them
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        torch.cuda.empty_cache()
+    return out
+
+
+def _config1(dev, cpu: bool) -> dict:
+    """Config 1: V256 C64 H4 L2 block 138, fp32, weights N(0, 0.02) seed 0; Gaussian random walk (seed 1, 96 points, the
+    last 90 as context so that 89 + 48 positions fit the block), order 1; predict_samples(100 trajectories, 48 points)."""
+    import pandas as pd
+
+    from diff_gpt_b200 import GPT, TemperatureSampler
+    from diff_gpt_b200.diff_gpt import DiffGPT
+
+    cfg = dict(vocab_size=256, n_embd=64, n_head=4, n_layer=2, block_size=138)
+    w = seeded_weights(cfg, 0, torch.float32)
+    walk = np.cumsum(np.random.default_rng(1).normal(0.0, 1.0, 96))
+    dom = host_codec().get_domain_of_definition(walk.reshape(-1, 1), 1, use_decimal=False)
+    df = pd.DataFrame(walk[-90:].reshape(-1, 1), columns=["y"])
+    n, h = 100, 48
+    dg = DiffGPT(model=load_into(GPT(**cfg), w, torch.float32, dev), order_of_derivative=1, domain_of_definition=dom, use_decimal=False)
+    fut = dg.predict_samples(df, max_new_points=h, num_samples=n, sampler=TemperatureSampler(1.0))
+    assert fut.shape == (n, h, 1) and np.isfinite(fut).all()
+    t = _wall(lambda: dg.predict_samples(df, max_new_points=h, num_samples=n, sampler=TemperatureSampler(1.0)), dev, repeat=10)
+    line = {"workload": "BASELINE config 1: DiffGPT.predict_samples, 100 trajectories x 48 points, fp32, 89-token prompt",
+            "value": n * h / t, "unit": "tokens/s", "ms_per_call": 1e3 * t, "us_per_decode_step": 1e6 * t / h, "dtype": "f32",
+            "bound": "launch latency (0.43 MB of weights, 137 cached positions): one graph replay per step",
+            "api": "DiffGPT.predict_samples(host frame) -> host float64 [100, 48, 1]"}
+    ref = reference_side()
+    if cpu and ref.available:
+        rdg = ref.DiffGPT(model=ref.model(cfg, w, torch.float32), order_of_derivative=1, domain_of_definition=dom, use_decimal=False)
+        rs = ref.TemperatureSampler(1.0)
+        rdg.predict_samples(df, max_new_points=h, num_samples=n, sampler=rs)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            rdg.predict_samples(df, max_new_points=h, num_samples=n, sampler=rs)
+        tc = (time.perf_counter() - t0) / 3
+        line["cpu"] = {"value": n * h / tc, "unit": "tokens/s", "kind": "reference", "cores": torch.get_num_threads(), "sample": "the same call, full size"}
+    return line
+
+
+def _config2(dev, cpu: bool) -> dict:
+    """Config 2: V512 C256 H8 (head_dim 32) L4 block 512, bf16, weights N(0, 0.02) seed 2; one causal forward of
+    256 sequences x 512 uniform-random tokens (seed 2) with the logit soft-cap."""
+    from diff_gpt_b200 import GPT, _lib
+
+    cfg = dict(vocab_size=512, n_embd=256, n_head=8, n_layer=4, block_size=512)
+    w = seeded_weights(cfg, 2, torch.bfloat16)
+    B, T, C, L, V = 256, 512, 256, 4, 512
+    idx = torch.randint(0, V, (B, T), generator=torch.Generator().manual_seed(2)).to(dev)
+    model = load_into(GPT(**cfg), w, torch.bfloat16, dev)
+    for _ in range(3):
+        logits = model(idx)[0]
+    assert logits.shape == (B, T, V)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    a.record()
+    for _ in range(5):
+        model(idx)
+    b.record()
+    torch.cuda.synchronize(dev)
+    ms = a.elapsed_time(b) / 5
+    timer = _lib.KernelTimer()
+    with _lib.timed(timer):
+        model(idx)
+    torch.cuda.synchronize(dev)
+    attn_ms = timer.summary()["dgpt_fmha_prefill"]["total_ms"]
+    attn_flops = 2.0 * B * T * T * C * L  # causal QK^T and PV over all layers
+    gemm_flops = 2.0 * B * T * (11 * C * C * L + C * V)
+    pk = peaks()
+    line = {"workload": "BASELINE config 2: batched causal forward, 256 x 512 tokens, bf16, head_dim 32", "value": ms, "unit": "ms per forward",
+            "tokens_per_s": B * T / ms * 1e3, "forward_tflops": (attn_flops + gemm_flops) / ms / 1e9,
+            "attention_ms": attn_ms, "attention_tflops": attn_flops / attn_ms / 1e9,
+            "attention_frac_of_bf16_peak": attn_flops / attn_ms / 1e9 / pk["bf16_tflops_sustained"], "peak": pk["bf16_tflops_sustained"],
+            "peak_source": pk["source"], "dtype": "bf16", "api": "GPT.forward(idx) -> logits [256, 512, 512]"}
+    del model, logits
+    ref = reference_side()
+    if cpu and ref.available:
+        rm = ref.model(cfg, w, torch.bfloat16)
+        small = idx[:8].cpu()
+        with torch.inference_mode():
+            rm(small)
+            t0 = time.perf_counter()
+            rm(small)
+            tc = time.perf_counter() - t0
+        line["cpu"] = {"value": 1e3 * tc * (B / 8), "unit": "ms per forward", "kind": "reference", "cores": torch.get_num_threads(),
+                       "sample": f"8 of the 256 sequences ({1e3 * tc:.0f} ms), scaled by 32"}
+    return line
+
+
+def cfg3_series(n_series: int, rows: int = 608) -> list[np.ndarray]:
+    """Config 3's frames: 7 channels, sum of 3 sinusoids (periods 12..168, amplitudes U(0.5, 2)) + AR(1) noise (phi 0.8, sd 0.1), seed 3."""
+    rng = np.random.default_rng(3)
+    out = []
+    for _ in range(n_series):
+        t = np.arange(rows)[:, None]
+        periods = rng.integers(12, 169, size=(3, 7))
+        amps = rng.uniform(0.5, 2.0, size=(3, 7))
+        x = sum(amps[i] * np.sin(2 * np.pi * t / periods[i]) for i in range(3))
+        e = rng.normal(0, 0.1, size=(rows, 7))
+        noise = np.zeros((rows, 7))
+        for i in range(1, rows):
+            noise[i] = 0.8 * noise[i - 1] + e[i]
+        out.append((x + noise).astype(np.float64))
+    return out
+
+
+def _config3(dev, cpu: bool) -> dict:
+    """Config 3: V1024 C512 H8 (head_dim 64) L6 block 4096, bf16, weights N(0, 0.02) seed 3; 64 series of 7 channels with
+    per-column orders [0,1,1,2,2,1,0], 512 context rows (3570 tokens) + 96 rows (672 steps), channels 5 and 6 forced
+    from the known future, argmax elsewhere; one trajectory per series, all 64 series in one decode."""
+    from diff_gpt_b200 import GPT, Engine, TemperatureSampler
+
+    cfg = dict(vocab_size=1024, n_embd=512, n_head=8, n_layer=6, block_size=4096)
+    w = seeded_weights(cfg, 3, torch.bfloat16)
+    orders = np.array([0, 1, 1, 2, 2, 1, 0])
+    codec = host_codec()
+    S, F, P, G = 64, 7, 3570, 672
+    prompts, scheds = [], []
+    for x in cfg3_series(S):
+        dom = codec.get_domain_of_definition(x, orders, use_decimal=False)
+        _, _, tok = codec.encode(inp=x, vocab_size=cfg["vocab_size"], domain_of_definition=dom, order_of_derivative=orders, use_decimal=False)
+        flat = tok.reshape(-1).astype(np.int64).tolist()
+        assert len(flat) == P + G
+        prompts.append(flat[:P])
+        scheds.append([flat[P + p] if (p % F) >= 5 else None for p in range(G)])
+    eng = Engine(load_into(GPT(**cfg), w, torch.bfloat16, dev))
+    sampler = TemperatureSampler(0.0)
+    toks, masks = eng.generate_many(prompts, 1, G, sampler, force_schedules=scheds)
+    assert toks.shape == (S, 1, G) and int(masks.sum()) == S * G * 5 // 7
+    t = _wall(lambda: eng.generate_many(prompts, 1, G, sampler, force_schedules=scheds), dev, repeat=2)
+    C, L = cfg["n_embd"], cfg["n_layer"]
+    params = L * (11 * C * C + 2 * C) + cfg["vocab_size"] * C
+    # every decode step reads each series' whole cache (no sharing across series): 2 (K, V) * L * C * 2 B per cached token
+    kv_bytes = sum(S * 2 * L * C * 2 * (P + g) for g in range(1, G))
+    algo = kv_bytes + (G - 1) * 2 * params
+    pk = peaks()
+    line = {"workload": "BASELINE config 3: 64 series x 1 trajectory, 3570-token prompts, 672 steps, channels 5-6 teacher-forced, bf16",
+            "value": S * G / t, "unit": "tokens/s", "ms_per_call": 1e3 * t, "dtype": "bf16",
+            "hbm": {"algorithmic_bytes_per_call": algo, "achieved_gbs": algo / t / 1e9, "frac_of_peak": algo / t / 1e9 / pk["hbm_gbs"],
+                    "peak": pk["hbm_gbs"], "peak_source": pk["source"], "note": "prefill of the 64 prompts is inside the timed call; its bytes and FLOPs are not counted"},
+            "api": "Engine.generate_many(64 host prompts, force_schedules) -> device tokens [64, 1, 672]"}
+    eng.release()
+    del eng
+    if cpu:
+        steps = 7
+        decode, kind = cpu_decoder(cfg, w, torch.bfloat16, None, 0.0)
+        t0 = time.perf_counter()
+        n = decode(prompts[0], 1, steps, scheds[0][:steps])
+        tc = time.perf_counter() - t0
+        line["cpu"] = {"value": n / tc, "unit": "tokens/s", "kind": kind, "cores": torch.get_num_threads(),
+                       "sample": f"one of the 64 series, prefill of 3570 tokens + {steps} of the 672 steps ({tc:.1f} s)"}
+    return line
 
 
 def prefill_attention(world: int, rank: int, dev, lengths=(4096, 8192, 16384, 32768)) -> list:
@@ -601,11 +826,48 @@ def prefill_attention(world: int, rank: int, dev, lengths=(4096, 8192, 16384, 32
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ta, tl = float(t[0]), float(t[1])
         flops = 2.0 * B * world * H * S * S * D
+        sdpa = sdpa_reference(q_rot.view(B, S, H, D).transpose(1, 2), cache[:, 0], cache[:, 1], y.view(B, S, H, D), flops / world) if rank == 0 else None
         out.append({"S": S, "batch": B * world, "attn_ms": ta, "layer_ms": tl, "attn_tflops": flops / ta / 1e9,
+                    "sdpa": sdpa,
                     "attn_tflops_per_gpu": flops / ta / 1e9 / world,
                     "frac_of_bf16_peak": flops / ta / 1e9 / world / pk["bf16_tflops"], "peak": pk["bf16_tflops"],
                     "peak_source": pk["source"]})
         del qkv, cache, q_rot, y, proj
+    return out
+
+
+def sdpa_reference(q, k, v, ours, flops: float) -> dict:
+    """`F.scaled_dot_product_attention(q, k, v, is_causal=True)` (the reference's call, mha.py:64) on the tensors the
+    attention kernel just read - q after RoPE and QK-norm [B, H, S, D] strided, K and V as cached - with torch's own
+    backend choice and with the cuDNN backend forced; TFLOP/s on this rank and the largest difference from `ours`."""
+    import torch.nn.functional as F
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    out = {}
+    for tag, backends in (("default", None), ("cudnn", [SDPBackend.CUDNN_ATTENTION])):
+        try:
+            def call():
+                if backends is None:
+                    return F.scaled_dot_product_attention(q, k, v, is_causal=True)
+                with sdpa_kernel(backends):
+                    return F.scaled_dot_product_attention(q, k, v, is_causal=True)
+
+            o = call()
+            call()
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(3):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                call()
+                b.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b))
+            diff = (o.transpose(1, 2).float() - ours.float()).abs().max().item()
+            out[tag] = {"ms": min(ts), "tflops": flops / min(ts) / 1e9, "max_abs_diff_from_ours": diff}
+            del o
+        except Exception as exc:  # noqa: BLE001 - a backend that refuses these strides is reported, not fatal
+            out[tag] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
     return out
 
 
@@ -799,6 +1061,8 @@ def main() -> None:
     ap.add_argument("--no-kernel-pass", action="store_true", help="skip the per-kernel timing step")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the config-5 prefill-attention sweep")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the lines for BASELINE configs 1, 2 and 3")
+    ap.add_argument("--no-reference-cuda", action="store_true", help="skip the reference's own torch-CUDA decode leg")
     ap.add_argument("--no-overlap", action="store_true",
                     help="run the shared-prompt attention phase before the per-row phase instead of beside it")
     ap.add_argument("--no-graph", action="store_true", help="launch the decode steps eagerly (for profilers)")

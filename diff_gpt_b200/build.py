@@ -25,7 +25,6 @@ FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
     "-Xptxas", "-v" if os.environ.get("DGPT_PTXAS_V") else "-O3",
-    *os.environ.get("DGPT_NVCC_FLAGS", "").split(),  # extra -D switches for tuning sweeps
 ]
 
 

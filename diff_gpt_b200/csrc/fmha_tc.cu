@@ -348,14 +348,6 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
 //   bar_p[b]  all 256 softmax threads have written P into b  (256 thread arrivals)
 //   bar_o[b]  the P V product of that tile is done            (tcgen05.commit)
 // so the softmax of tile j overlaps P V of tile j-1 and Q K^T of tile j+1.  One CTA per SM (512 TMEM columns).
-#ifdef DGPT_TC_PROF
-__device__ long long g_prof[16];
-#define PROF_T(k) const long long prof_t##k = clock64()
-#define PROF_ADD(i, a, b) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 33 || tid == 256)) g_prof[i] += prof_t##b - prof_t##a; } while (0)
-#else
-#define PROF_T(k)
-#define PROF_ADD(i, a, b)
-#endif
 constexpr int kWsThreads = 320;  // 8 softmax warps, the MMA issuer's warp, the loader's warp
 constexpr uint32_t kWsTmemCols = 512;
 
@@ -543,13 +535,10 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         const bool next_s = j + 2 < n_tiles;
         // P_j is complete when every row has arrived; by then every row has also consumed S_j, so the same
         // buffer can take S_{j+2} at once (P lives in its own columns)
-        PROF_T(10);
         ok = wait_or_abort(bar_p0 + 8 * buf, ph, abort_flag, 20);
-        PROF_T(11);
         ok = ok && wait_or_abort(bar_v0 + 8 * buf, ph, abort_flag, 21);
         if (ok && next_s) ok = wait_or_abort(bar_k0 + 8 * ((j + 2) % 3), (uint32_t)(((j + 2) / 3) & 1), abort_flag, 22);
         if (!ok) break;
-        PROF_T(12);
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < kStepsPV; ++ks)
@@ -561,10 +550,6 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           issue_s(buf, (j + 2) % 3);
           last_s[buf] = (int)(ph ^ 1u);
         }
-        PROF_T(13);
-        PROF_ADD(6, 10, 11);
-        PROF_ADD(7, 11, 12);
-        PROF_ADD(8, 12, 13);
       }
       if (!ok) {
         if (!*abort_flag) *abort_flag = 2;
@@ -609,7 +594,6 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       const int buf = j & 1;
       const uint32_t ph = (uint32_t)((j >> 1) & 1);
       const int t0 = j * kBN;
-      PROF_T(0);
       // exits are taken by whole warps (the vote makes the decision uniform), never by single lanes
       if (!__all_sync(0xffffffffu, wait_or_abort(bar_s0 + 8 * buf, ph, abort_flag, 23))) {
         fail = true;
@@ -636,11 +620,9 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       const int last_key = p.causal ? min(klen - 1, p.q_offset + q0 + row) : klen - 1;
       const int c0 = t0 + half * kHalf;  // key index of this thread's first column
       float sv[kHalf];
-      PROF_T(1);
 #pragma unroll
       for (int c = 0; c < kHalf / 32; ++c) tmem_ld32_nowait(lane_addr + buf * 128 + half * kHalf + c * 32, &sv[c * 32]);
       tc_wait_ld();
-      PROF_T(2);
       float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
@@ -684,7 +666,6 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         }
       }
       const float m_use = (m == -INFINITY) ? 0.f : m;
-      PROF_T(3);
       float rs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < kHalf / 32; ++c) {
@@ -700,19 +681,9 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         tmem_st16(lane_addr + kPCol + buf * 64 + half * (kHalf / 2) + c * 16, packed);
       }
       l = l * alpha + ((rs[0] + rs[1]) + (rs[2] + rs[3]));  // sum over this thread's columns only
-      PROF_T(4);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p0 + 8 * buf);
-      PROF_T(5);
-      PROF_ADD(0, 0, 1);
-      PROF_ADD(1, 1, 2);
-      PROF_ADD(2, 2, 3);
-      PROF_ADD(3, 3, 4);
-      PROF_ADD(4, 4, 5);
-#ifdef DGPT_TC_PROF
-      if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 33) g_prof[5] += 1;
-#endif
     }
     // every warp leaves the loop as a whole (waits are on CTA-wide events), so the collective loads below are safe
     if (!fail && n_tiles > 0) {
@@ -781,16 +752,6 @@ static bool encode_map(CUtensorMap* map, const void* base, const cuuint64_t (&di
 }
 
 }  // namespace tc
-
-#ifdef DGPT_TC_PROF
-extern "C" int dgpt_debug_prof(long long* out, int reset) {
-  if (reset) {
-    long long z[16] = {0};
-    return (int)cudaMemcpyToSymbol(tc::g_prof, z, sizeof(z));
-  }
-  return (int)cudaMemcpyFromSymbol(out, tc::g_prof, 16 * sizeof(long long));
-}
-#endif
 
 bool fmha_tc_supported(const FmhaArgs& a, const dgpt_kv_layout& kv) {
   if (a.dtype != DGPT_BF16 || (a.D != 64 && a.D != 128)) return false;

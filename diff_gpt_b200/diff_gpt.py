@@ -7,8 +7,9 @@ the Monte-Carlo trajectories come from one device-resident decode, and all
 trajectories are turned back into values by one vectorised integration instead of a
 Python loop over samples (diff_gpt.py:239-252).
 
-Training (`train`, `train_numa`) and `anomaly_scores` belong to other parts of the
-reference and are not provided here.
+`anomaly_scores` (diff_gpt.py:295-363) is provided too: one prefill and a fused log-softmax +
+gather.  Training (`train`, `train_numa`) belongs to another part of the reference and is not
+provided here.
 """
 
 from __future__ import annotations
@@ -39,6 +40,9 @@ def _quantile_of_sorted(ordered: torch.Tensor, q: float) -> torch.Tensor:
     return a + diff * t
 
 
+DEVICE_CODEC_MAX_ORDER = 8  # dgpt_encode_series / dgpt_integrate_tokens keep this many difference levels per column
+
+
 class DiffGPT:
     __slots__ = ("model", "order_of_derivative", "domain_of_definition", "use_decimal", "_engine")
 
@@ -64,6 +68,11 @@ class DiffGPT:
         arr = np.asarray(order)
         assert arr.shape == (n_cols,), f"order_of_derivative shape {arr.shape} must match {label} {n_cols}"
         return int(arr.max())
+
+    def _device_codec(self, n_cols: int) -> bool:
+        """True when values <-> tokens can run on the device: this package's GPT, and difference orders the device
+        codec covers.  Higher orders take the host codec (any order), then the same device decode of the tokens."""
+        return isinstance(self.model, GPT) and self._max_order(n_cols, "columns") <= DEVICE_CODEC_MAX_ORDER
 
     def _encode(self, values: np.ndarray):
         return encode(
@@ -149,6 +158,7 @@ class DiffGPT:
         series s draws the random stream keyed by (s, n); `predict_samples` is the case S = 1."""
         assert isinstance(self.model, GPT), "predict_samples_many needs the diff_gpt_b200 GPT"
         assert len(dfs) > 0
+        assert self._device_codec(dfs[0].shape[1]), f"difference orders above {DEVICE_CODEC_MAX_ORDER}: call predict_samples per frame"
         shape = dfs[0].shape
         for df in dfs:
             assert df.shape == shape, "all frames must have the same shape"
@@ -160,7 +170,7 @@ class DiffGPT:
         """(num_samples, max_new_points, n_features) float64: the forecast rows only."""
         self._check_future_request(df, max_new_points, num_samples)
         rows, columns = df.shape
-        if isinstance(self.model, GPT):
+        if self._device_codec(columns):
             return self._future_samples_on_device(df, max_new_points, sampler, num_samples).cpu().numpy()
         start, scale, encoded = self._encode(df.to_numpy(dtype=np.float64))
         prompt = encoded.reshape(-1).astype(np.int64).tolist()  # row-major: (time, channel)
@@ -186,7 +196,7 @@ class DiffGPT:
     ) -> dict[float, pd.DataFrame]:
         for q in quantiles:
             assert 0.0 < q < 1.0, f"quantile {q} must be in (0, 1)"
-        if isinstance(self.model, GPT):
+        if self._device_codec(df.shape[1]):
             self._check_future_request(df, max_new_points, num_samples)
             futures = self._future_samples_on_device(df, max_new_points, sampler, num_samples)
             ordered = torch.sort(futures, dim=0).values  # (N, H, F) sorted over the trajectories
@@ -279,7 +289,7 @@ class DiffGPT:
             f"chunk the input manually for longer sequences"
         )
         device = torch.device(self.model.device_type)
-        if isinstance(self.model, GPT):  # tokenised where the model lives
+        if self._device_codec(columns):  # tokenised where the model lives
             tokens = self._encode_on_device(inp[None])[0].reshape(1, N).to(torch.int64)
         else:
             _, _, encoded = self._encode(inp)

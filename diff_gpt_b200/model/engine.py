@@ -28,7 +28,7 @@ import torch
 
 from .. import _lib, ops
 from ..sampler.sampler import Sampler
-from .gpt import GPT, BaseGPT, ForwardPlan, KvBinding, _pick_splits
+from .gpt import GPT, BaseGPT, ForwardPlan, KvBinding, _pick_splits  # noqa: F401
 from .kv_cache import KVCache, PagedKVCache
 
 SHARED_PREFIX_MIN_ROWS = 16  # below this the prompt is read by the per-row kernel (split along keys)
@@ -50,13 +50,13 @@ class DecodeRun:
 
     @staticmethod
     def key_for(model, prompt_lens, num_samples, max_tokens, sampler, seed, has_force, page_tokens, use_graph,
-                fmha_impl, overlap_prefix) -> tuple:
+                fmha_impl, overlap_prefix, shared_prefix=None) -> tuple:
         spec = (1.0, 1.0) if sampler is None else (sampler.native_spec() if isinstance(sampler, Sampler) else None)
         emb = model.token_embedding_table.weight
         return (
             id(model), str(emb.device), emb.dtype, tuple(prompt_lens), num_samples, max_tokens, spec,
             None if spec is not None else id(sampler), seed, has_force, page_tokens, use_graph, fmha_impl,
-            overlap_prefix,
+            overlap_prefix, shared_prefix,
         )
 
     def __init__(
@@ -75,6 +75,7 @@ class DecodeRun:
         fmha_impl: int = 0,
         kv_pool: torch.Tensor | None = None,
         overlap_prefix: bool = True,
+        shared_prefix: bool | None = None,
     ) -> None:
         self.model = model
         emb = model.token_embedding_table.weight
@@ -100,7 +101,7 @@ class DecodeRun:
         self.prompt_lens = lens
         self.key = self.key_for(
             model, lens, N, G, sampler, seed, force_schedules is not None, page_tokens, use_graph, fmha_impl,
-            overlap_prefix,
+            overlap_prefix, shared_prefix,
         )
         self.packed = model.packed_weights()  # the graph holds these tensors' addresses
         self.cache = PagedKVCache(L, H, D, S, N, max(lens), G, dt, dev, page_tokens=page_tokens, pool=kv_pool)
@@ -134,7 +135,9 @@ class DecodeRun:
             self.prefills.append((P, members, idx, bind, plan, table))
 
         # ---- decode plan ----
-        shared = N >= SHARED_PREFIX_MIN_ROWS
+        # A shard of a larger job takes the path the whole job would take (the two paths round differently), so the
+        # caller may decide; by default the prompt is shared from SHARED_PREFIX_MIN_ROWS trajectories per series on.
+        shared = (N >= SHARED_PREFIX_MIN_ROWS) if shared_prefix is None else bool(shared_prefix)
         slot0 = torch.full((self.R,), self.cache.suffix_slot0, dtype=torch.int32, device=dev)
         self.bind = KvBinding(
             layouts=[self.cache.row_layout(l) for l in range(L)],
@@ -318,6 +321,7 @@ class Engine:
         use_graph: bool = True,
         fmha_impl: int = 0,
         overlap_prefix: bool = True,
+        shared_prefix: bool | None = None,
     ) -> tuple[torch.Tensor, torch.Tensor]:
         """Decode every prompt `num_samples` times.
 
@@ -327,7 +331,10 @@ class Engine:
 
         Returns (tokens, masks): int32 device tensors of shape (S, num_samples, G); masks are 1 where a
         token was sampled and 0 where it was forced.  `traj_offset`/`series_offset` shift the ids that key
-        the random stream, so a shard of the trajectories reproduces exactly its part of the full run.
+        the random stream, so a shard of the trajectories reproduces exactly its part of the full run;
+        `shared_prefix` (None = decide from `num_samples`) fixes whether the prompt's keys are read once per series
+        by the tensor-core phase or per row, so that a shard can take the path the whole job takes.
+        `num_samples == 0` (a rank without work) returns empty tensors.
         """
         assert isinstance(self.model, GPT), "generate_many needs the diff_gpt_b200 GPT"
         assert len(prompts) > 0 and all(len(p) > 0 for p in prompts), "tokens must be non-empty"
@@ -336,8 +343,8 @@ class Engine:
         G = min(_effective_max_tokens(self.model.block_size, len(p), max_tokens) for p in prompts)
         S = len(prompts)
         dev = self.model.token_embedding_table.weight.device
-        if G == 0:
-            z = torch.zeros((S, num_samples, 0), dtype=torch.int32, device=dev)
+        if G == 0 or num_samples == 0:
+            z = torch.zeros((S, num_samples, G), dtype=torch.int32, device=dev)
             return z, z.clone()
         if force_schedules is not None:
             assert len(force_schedules) == S
@@ -349,7 +356,7 @@ class Engine:
         lens = [int(prompts.shape[1])] * S if on_device else [len(p) for p in prompts]
         key = DecodeRun.key_for(
             self.model, lens, num_samples, G, sampler, seed, force_schedules is not None, page_tokens, use_graph,
-            fmha_impl, overlap_prefix,
+            fmha_impl, overlap_prefix, shared_prefix,
         )
         run = self._run
         if run is not None and run.key == key and run.reusable():
@@ -359,7 +366,7 @@ class Engine:
             run = DecodeRun(
                 self.model, prompts, num_samples, G, sampler, seed, force_schedules, traj_offset=traj_offset,
                 series_offset=series_offset, page_tokens=page_tokens, use_graph=use_graph, fmha_impl=fmha_impl,
-                overlap_prefix=overlap_prefix,
+                overlap_prefix=overlap_prefix, shared_prefix=shared_prefix,
             )
             self._run = run
         run.start()
@@ -422,6 +429,9 @@ class Engine:
         self, tokens: list[int], num_samples: int = 1, **kwargs
     ) -> tuple[list[list[int]], list[list[int]]]:
         """All trajectories at once: (results, masks), prompt included, masks 0 on prompt/forced positions."""
+        unknown = set(kwargs) - {"max_tokens", "sampler", "seed", "force_schedule"}
+        if unknown:  # the reference forwards **kwargs to generate(), whose signature rejects anything else
+            raise TypeError(f"generate() got an unexpected keyword argument {sorted(unknown)[0]!r}")
         results = [list(tokens) for _ in range(num_samples)]
         masks = [[0] * len(tokens) for _ in range(num_samples)]
         if isinstance(self.model, GPT) and isinstance(tokens, list) and len(tokens) > 0 and all(

@@ -493,10 +493,24 @@ class GPT(BaseGPT):
         return str(self.freqs_cis.device.type)
 
 
+_SM_COUNT: dict[int, int] = {}
+
+
+def _sm_count() -> int:
+    """Multiprocessors of the current CUDA device (148 on a B200); that figure is assumed where no device is present,
+    so the split policy can be examined on a CPU box."""
+    if not torch.cuda.is_available():
+        return 148
+    dev = torch.cuda.current_device()
+    if dev not in _SM_COUNT:
+        _SM_COUNT[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return _SM_COUNT[dev]
+
+
 def _pick_splits(n_pairs: int, n_keys: int) -> int:
-    """Split the keys when (row, head) pairs alone cannot fill the GPU (148 SMs x 16 warps)."""
-    target_warps = 148 * 16
-    if n_pairs >= target_warps or n_keys < 512:
+    """Split the keys when (row, head) pairs alone cannot fill the GPU (16 warps on every multiprocessor)."""
+    target_warps = _sm_count() * 16
+    if n_pairs <= 0 or n_pairs >= target_warps or n_keys < 512:
         return 1
     return max(1, min(-(-target_warps // n_pairs), n_keys // 256, 64))
 

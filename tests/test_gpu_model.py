@@ -526,3 +526,57 @@ def test_gpt_generate_without_cache_matches_the_engine_under_argmax():
     assert out[0, len(prompt) :].tolist() == ref[0].tolist()
     longer = m.generate(torch.tensor([prompt], device="cuda"), room + 5, TemperatureSampler(1.0), seed=3)
     assert longer.shape == (1, m.block_size + 5) and int(longer.min()) >= 0 and int(longer.max()) < m.vocab_size
+
+
+def test_generate_batch_rejects_unknown_keywords():
+    """The reference forwards **kwargs to generate(), so a misspelt keyword is a TypeError there (engine.py:156-169)."""
+    from diff_gpt_b200 import Engine
+
+    g = load_golden("small_fp32")
+    m = _model(g["meta"], golden_weights(g, torch.float32), torch.float32)
+    with pytest.raises(TypeError, match="max_token"):
+        Engine(m).generate_batch([1, 2, 3], num_samples=2, max_token=4)
+
+
+def test_shards_below_the_sharing_threshold_follow_the_whole_jobs_path():
+    """24 trajectories decoded as 12 + 12 (each below the 16-row threshold of the shared-prompt phase) with the
+    whole job's path handed down equal the 24 decoded at once, token for token; an empty shard returns empty tensors."""
+    from diff_gpt_b200 import Engine, NucleusSampler, TemperatureSampler
+
+    g = load_golden("small_bf16_d64")
+    m = _model(g["meta"], golden_weights(g, torch.float32), torch.bfloat16)
+    prompts = [g["idx"][0].tolist(), g["idx"][1].tolist()]
+    s = NucleusSampler(0.9, TemperatureSampler(1.0))
+    eng = Engine(m)
+    whole, _ = eng.generate_many(prompts, 24, 10, s, seed=11)
+    lo, _ = eng.generate_many(prompts, 12, 10, s, seed=11, traj_offset=0, shared_prefix=True)
+    hi, _ = eng.generate_many(prompts, 12, 10, s, seed=11, traj_offset=12, shared_prefix=True)
+    assert torch.equal(torch.cat([lo, hi], dim=1), whole)
+    none, masks = eng.generate_many(prompts, 0, 10, s, seed=11, traj_offset=24)
+    assert none.shape == (2, 0, 10) and masks.shape == (2, 0, 10)
+
+
+def test_difference_order_above_the_device_codec_takes_the_host_codec():
+    """Order 9 (the reference accepts any order in float64): predict_samples tokenises and decodes on the host and
+    still decodes the trajectories on the device; under argmax every trajectory equals the host-side restatement."""
+    import pandas as pd
+
+    from diff_gpt_b200 import TemperatureSampler
+    from diff_gpt_b200.diff_gpt import DiffGPT
+    from diff_gpt_b200.encoder_decoder import decode, encode, get_domain_of_definition
+
+    g = load_golden("small_fp32")
+    w = golden_weights(g, torch.float32)
+    m = _model(g["meta"], w, torch.float32)  # block_size 16
+    x = np.cumsum(np.random.default_rng(5).normal(0, 1, (14, 1)), axis=0)
+    dom = get_domain_of_definition(x, 9, use_decimal=False)
+    dg = DiffGPT(model=m, order_of_derivative=9, domain_of_definition=dom, use_decimal=False)
+    df = pd.DataFrame(x, columns=["y"])
+    fut = dg.predict_samples(df, max_new_points=4, num_samples=3, sampler=TemperatureSampler(0.0))
+    assert fut.shape == (3, 4, 1) and np.isfinite(fut).all()
+    start, scale, tok = encode(inp=x, vocab_size=64, domain_of_definition=dom, order_of_derivative=9, use_decimal=False)
+    prompt = tok.reshape(-1).astype(np.int64).tolist()
+    ref, _, _ = ref_decode.mc_decode(_shape(g["meta"]), w, prompt, 1, 4, temperature=0.0)
+    full = np.asarray(prompt + ref[0].tolist(), dtype=np.int64).reshape(1, -1, 1)
+    want = decode(start=start, scale=scale, inp=full, vocab_size=64, order_of_derivative=9, use_decimal=False)[0, 14:18]
+    assert np.array_equal(fut[0], want) and np.array_equal(fut[1], want)
