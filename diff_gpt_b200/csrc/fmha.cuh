@@ -18,6 +18,25 @@ struct FmhaArgs {
   int* status;
   int max_ctas;  // two-CTAs-per-SM kernel only: at most this many CTAs, looping over the query tiles (0 = one CTA per tile)
   int two_cta;  // tensor-core path only: the 128-thread kernel with two CTAs per SM instead of the warp-specialised one
+  int pingpong;  // tensor-core path only: the kernel with two query tiles per CTA
+};
+
+// What the tensor-core kernels need besides the three tensor maps.
+struct TcParams {
+  const int* kv_len;
+  int kv_len_all;
+  const int* page_table;
+  int max_pages;
+  int page_tokens;
+  void* o;
+  long long o_bs, o_rs;
+  int o_f32;
+  float* lse;
+  int H, Tq, q_offset, causal;
+  float scale_log2;
+  int* status;
+  int n_qt, n_work;  // query tiles per (batch, head) and work items in all (a capped grid loops over them)
+  int BH, group_bh;  // two-query-tile kernel: (batch, head) pairs in all, and how many are worked on at a time
 };
 
 // warp-level kernel (fmha_simt.cu)
@@ -26,5 +45,8 @@ int fmha_simt(const FmhaArgs& a, const KvView& kv, cudaStream_t st);
 // tcgen05 / TMEM kernel (fmha_tc.cu)
 bool fmha_tc_supported(const FmhaArgs& a, const dgpt_kv_layout& kv);
 int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st);
+// the same with two query tiles per CTA taking turns on the tensor cores (fmha_pp.cu); `tp` and the maps come from fmha_tc
+struct TcMaps;
+int fmha_tc_pp_launch(const FmhaArgs& a, const TcMaps& maps, TcParams p, long long kv_span, cudaStream_t st);
 
 }  // namespace dgpt

@@ -33,31 +33,8 @@
 namespace dgpt {
 namespace tc {
 
-constexpr int kBM = 128;          // queries per CTA
-constexpr int kBN = 128;          // keys per tile
 constexpr int kTmemCols = 256;    // S/P: [0,128), O tile: [128, 128 + D)
 
-// Instruction descriptor: bf16 x bf16 -> fp32, M = 128.
-__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
-         ((uint32_t)(kBM >> 4) << 24);
-}
-
-struct Params {
-  const int* kv_len;
-  int kv_len_all;
-  const int* page_table;
-  int max_pages;
-  int page_tokens;
-  void* o;
-  long long o_bs, o_rs;
-  int o_f32;
-  float* lse;
-  int H, Tq, q_offset, causal;
-  float scale_log2;
-  int* status;
-  int n_qt, n_work;  // query tiles per (batch, head) and work items in all (two-CTAs-per-SM kernel: CTAs loop over them)
-};
 
 template <int D>
 __global__ void __launch_bounds__(128, 2)
@@ -734,21 +711,6 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, kWsTmemCols);
-}
-
-// ---- host side -------------------------------------------------------------------------
-// 4-D bf16 tensor map with a [rows][64] box, 128-byte swizzle; dim 0 is the head dimension.
-static bool encode_map(CUtensorMap* map, const void* base, const cuuint64_t (&dims)[4], const cuuint64_t (&strides)[3],
-                       const cuuint32_t (&box)[4]) {
-  const cuuint32_t ones[4] = {1, 1, 1, 1};
-  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, ones,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    set_error("fmha_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
-    return false;
-  }
-  return true;
 }
 
 }  // namespace tc

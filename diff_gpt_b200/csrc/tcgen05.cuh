@@ -185,6 +185,15 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   return false;
 }
 
+constexpr int kBM = 128;  // query rows per MMA (the M of every tcgen05.mma here)
+constexpr int kBN = 128;  // keys per tile
+
+// Instruction descriptor: bf16 x bf16 -> fp32, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(kBM >> 4) << 24);
+}
+
 // ---- host side -------------------------------------------------------------------------
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -200,6 +209,20 @@ inline EncodeFn encode_fn() {
     return reinterpret_cast<EncodeFn>(p);
   }();
   return fn;
+}
+
+// 4-D bf16 tensor map with a [rows][64] box, 128-byte swizzle; dim 0 is the head dimension.
+inline bool encode_map(CUtensorMap* map, const void* base, const cuuint64_t (&dims)[4], const cuuint64_t (&strides)[3],
+                       const cuuint32_t (&box)[4]) {
+  const cuuint32_t ones[4] = {1, 1, 1, 1};
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, ones,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("fmha_tc: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return false;
+  }
+  return true;
 }
 
 inline bool device_is_sm100() {
