@@ -189,8 +189,9 @@ extern "C" int dgpt_fmha_prefill(const void* q, int64_t q_batch_stride, int64_t 
   DGPT_REQUIRE(kv_len || kv_len_all >= 0, "fmha_prefill: kv length missing");
   DGPT_REQUIRE(q_row_stride % 8 == 0 && q_batch_stride % 8 == 0 && o_row_stride % 8 == 0 && o_batch_stride % 8 == 0,
                "fmha_prefill: strides must be multiples of 8 elements");
-  DGPT_REQUIRE(impl >= 0 && impl <= 3,
-               "fmha_prefill: impl must be 0 (auto), 1 (warp-level), 2 (tensor-core) or 3 (tensor-core, two CTAs per SM)");
+  DGPT_REQUIRE(impl >= 0 && impl <= 4,
+               "fmha_prefill: impl must be 0 (auto), 1 (warp-level), 2 (tensor-core, one query tile per CTA), 3 (tensor-core, "
+               "two CTAs per SM) or 4 (tensor-core, two query tiles per CTA)");
   if (int e = validate_kv(kv, D)) return e;
   if (B == 0 || Tq == 0) return DGPT_OK;
   FmhaArgs a;
@@ -208,6 +209,7 @@ extern "C" int dgpt_fmha_prefill(const void* q, int64_t q_batch_stride, int64_t 
   const long long span = causal ? (long long)Tq + q_offset
                                 : (kv_len ? (long long)kv->max_pages * kv->page_tokens : (long long)kv_len_all);
   a.two_cta = impl == 3 || (impl == 0 && span < 4096);
+  a.pingpong = impl == 4;
   if (impl >= 2 && !tc_ok) {
     set_error("fmha_prefill: the tensor-core kernel does not cover dtype %d, head_dim %d with this layout", dtype, D);
     return DGPT_E_UNSUPPORTED;

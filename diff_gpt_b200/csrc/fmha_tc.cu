@@ -39,7 +39,7 @@ constexpr int kTmemCols = 256;    // S/P: [0,128), O tile: [128, 128 + D)
 template <int D>
 __global__ void __launch_bounds__(128, 2)
 fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
-               const __grid_constant__ CUtensorMap mv, const Params p) {
+               const __grid_constant__ CUtensorMap mv, const TcParams p) {
   constexpr int kSub = D / 64;                  // 64-element (128-byte) column blocks per row
   constexpr uint32_t kSubBytes = kBN * 128;     // one [128 rows][64 bf16] swizzled block
   constexpr uint32_t kTileBytes = kSub * kSubBytes;
@@ -331,7 +331,7 @@ constexpr uint32_t kWsTmemCols = 512;
 template <int D>
 __global__ void __launch_bounds__(kWsThreads, 1)
 fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
-                  const __grid_constant__ CUtensorMap mv, const Params p) {
+                  const __grid_constant__ CUtensorMap mv, const TcParams p) {
   constexpr int kSub = D / 64;
   constexpr uint32_t kSubBytes = kBN * 128;
   constexpr uint32_t kTileBytes = kSub * kSubBytes;
@@ -730,7 +730,8 @@ bool fmha_tc_supported(const FmhaArgs& a, const dgpt_kv_layout& kv) {
 int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
   using namespace tc;
   const int D = a.D;
-  CUtensorMap mq, mk, mv;
+  TcMaps maps;
+  CUtensorMap &mq = maps.q, &mk = maps.k, &mv = maps.v;
   {
     const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)a.H, (cuuint64_t)a.Tq, (cuuint64_t)a.B};
     const cuuint64_t q_bs = a.q_bs > 0 ? (cuuint64_t)a.q_bs : (cuuint64_t)a.q_rs * a.Tq;
@@ -747,7 +748,7 @@ int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
     if (!encode_map(&mk, kv.k_base, dims, strides, box)) return DGPT_E_CUDA;
     if (!encode_map(&mv, kv.v_base, dims, strides, box)) return DGPT_E_CUDA;
   }
-  Params p;
+  TcParams p;
   p.kv_len = a.kv_len;
   p.kv_len_all = a.kv_len_all;
   p.page_table = kv.page_table;
@@ -766,6 +767,13 @@ int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
   p.status = a.status;
   p.n_qt = (a.Tq + kBM - 1) / kBM;
   p.n_work = p.n_qt * a.H * a.B;
+  p.BH = a.B * a.H;
+  p.group_bh = p.BH;
+  if (a.pingpong) {
+    const long long span = a.causal ? (long long)a.Tq + a.q_offset
+                                    : (a.kv_len ? (long long)kv.max_pages * kv.page_tokens : (long long)a.kv_len_all);
+    return fmha_tc_pp_launch(a, maps, p, span, st);
+  }
   dim3 grid((unsigned)p.n_qt, (unsigned)a.H, (unsigned)a.B);
   // >= 80 KB per CTA keeps residency at two CTAs per SM, which is what the 2 x 256 TMEM columns allow
   size_t smem = (size_t)3 * (D / 64) * kBN * 128 + 64 + 1024;

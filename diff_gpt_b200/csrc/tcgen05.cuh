@@ -7,6 +7,12 @@
 #include "common.cuh"
 
 namespace dgpt {
+
+// The three tensor maps of an attention launch (Q, K pool, V pool).
+struct TcMaps {
+  CUtensorMap q, k, v;
+};
+
 namespace tc {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -57,7 +57,7 @@ def _run(D, B, H, Tq, Tk, pt, causal, q_offset, use_table, o_f32, impl=2, seed=0
         assert (lse[b : b + 1].cpu() - want_lse).abs().max().item() <= 2e-2
 
 
-IMPLS = [2, 3]  # 2 = warp-specialised kernel, 3 = two CTAs per SM
+IMPLS = [2, 3, 4]  # 2 = warp-specialised kernel, 3 = two CTAs per SM, 4 = two query tiles per CTA
 
 
 @pytest.mark.parametrize("impl", IMPLS)
