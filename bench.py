@@ -949,11 +949,12 @@ def kernel_case(name: str, iters: int = 8) -> None:
 
         work = R * (2 * C * 2 * own + 3 * C * 2 + C * 4 + H * 4)
         unit, peak = "GB/s", pk["hbm_gbs"]
-    elif name in ("fmha", "fmha_long"):
+    elif name in ("fmha", "fmha_long", "fmha_pair"):
         # config-5 shapes; "fmha" = S 4096 on the two-CTAs-per-SM kernel (the one used below 4096 keys and for the
-        # shared-prompt phase), "fmha_long" = S 8192 on the warp-specialised one (used from 4096 keys on)
+        # shared-prompt phase), "fmha_long" = S 8192 on the warp-specialised one, "fmha_pair" = S 8192 on the kernel
+        # with two query tiles per CTA
         B, H, S, D = 8, 16, (4096 if name == "fmha" else 8192), 128
-        which = 3 if name == "fmha" else 2
+        which = {"fmha": 3, "fmha_long": 2, "fmha_pair": 4}[name]
         q = torch.randn((B, S, H, D), device=dev, dtype=torch.bfloat16, generator=g)
         kv = torch.randn((B, 2, H, S, D), device=dev, dtype=torch.bfloat16, generator=g)
         lay = ops.kv_layout(kv[0, 0], kv[0, 1], 2 * H * S * D, S * D, S)
@@ -1051,7 +1052,7 @@ def kernel_case(name: str, iters: int = 8) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel-case", default=None, choices=["decode_attn", "fmha", "fmha_long", "sample", "depthmix", "fmha_prefix", "linear"],
+    ap.add_argument("--kernel-case", default=None, choices=["decode_attn", "fmha", "fmha_long", "fmha_pair", "sample", "depthmix", "fmha_prefix", "linear"],
                     help="run one kernel alone on a small case (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)

@@ -36,6 +36,8 @@ struct TcParams {
   float scale_log2;
   int* status;
   int n_qt, n_work;  // query tiles per (batch, head) and work items in all (a capped grid loops over them)
+  int d_head;        // head_dim of the tensors in global memory (32 rides on the 64-wide kernels: the TMA boxes are 64 wide
+                     // and the columns past the tensor's extent arrive as zeros, so scores and outputs are unchanged)
   int BH, group_bh;  // two-query-tile kernel: (batch, head) pairs in all, and how many are worked on at a time
 };
 

@@ -1,7 +1,7 @@
 // tcgen05 / TMEM attention with TWO query tiles per CTA taking turns on the tensor cores (sm_100a, bf16,
 // head_dim 64 or 128): causal / chunk prefill and the shared-prompt phase of the Monte-Carlo decode.
 //
-// One persistent CTA of 320 threads per SM works through (query-tile pair, head, batch) items.  A pair is
+// One persistent CTA of 384 threads per SM works through (query-tile pair, head, batch) items.  A pair is
 // 2 x 128 query rows of one (batch, head); both tiles meet the same K/V tiles, so every K/V tile brought into
 // shared memory feeds four MMAs instead of two, and while the softmax threads of one tile turn its scores into
 // probabilities the tensor cores work on the other tile.
@@ -10,14 +10,30 @@
 //                    ahead of the consumers across item boundaries, so the next item's Q, K0 and V0 arrive while
 //                    the current item's last tiles are still being worked on
 //   warp 8, lane 0   issuer, per key tile j:  O0 += P0_j V_j;  S0 = Q0 K_{j+1}^T;  O1 += P1_j V_j;  S1 = Q1 K_{j+1}^T
-//                    (each product waits only for what it needs: P of its tile, the K or V slot)
-//   warps 0-3 / 4-7  softmax of query tile 0 / 1, one thread per query row: tcgen05.ld of the row's 128 scores,
-//                    running maximum with lazy rescaling (O in TMEM is touched only when the maximum moved by
-//                    more than 2^8), exp2, packed bf16 P written over the scores it came from (tcgen05.st), one
-//                    mbarrier arrival per row; at the end of an item the row normalises its O and stores it
+//                    (each product waits only for what it needs: P of its tile, the K or V slot).  The eight MMAs of a
+//                    product are one asm statement with constant descriptor steps: this lane shares its scheduler
+//                    with two busy softmax warps, and every instruction it does not execute is time the tensor pipe
+//                    does not wait for.
+//   warps 0-3 / 4-7  softmax of query tile 0 / 1, one thread per query row: tcgen05.ld of the row's 128 scores; from
+//                    the second key tile on the probabilities are taken against the running maximum at once, the
+//                    tile's own maximum is found in the same sweep, and only a score more than 2^8 above the running
+//                    maximum sends the tile through the careful path (maximum first, O in TMEM rescaled); one pair
+//                    of exponentials in four is computed on the FMA pipe (range reduction + cubic) to take load off
+//                    the exp2 unit; packed bf16 P is written over the scores it came from (tcgen05.st), one mbarrier
+//                    arrival per row; at the end of an item the row normalises its O and stores it
+//   warps 10-11      idle: they make the helper warps a whole warpgroup, so that it can hand registers to the softmax
+//                    warpgroups (setmaxnreg: 216 per softmax thread, 72 per helper thread)
 // TMEM columns: S0 / P0 [0,128)   S1 / P1 [128,256)   O0 [256, 256 + D)   O1 [384, 384 + D).
 // P_t overwrites S_t, so S_t of the next key tile is issued behind the P_t V product of this one; the tensor
 // pipe runs the MMAs of one thread in issue order, which is what makes the overwrite safe.
+//
+// What bounds it (measured on a B200, config-5 shapes): each query tile is one chain S -> softmax -> P V -> next S;
+// the chains of the two tiles interleave, but every change between a product with A in shared memory (Q K^T) and one
+// with A in TMEM (P V) drains the tensor pipe for about 250 cycles, four times per key tile, and a row's 128
+// exponentials keep its thread busy for about 1700 cycles while the exp2 unit is shared with the other tile's warp.
+// The kernel reaches 700 / 820 / 815 TFLOP/s at S = 4096 / 8192 / 16384 against 765 / 917 / 1000 for the kernel with one
+// query tile per CTA and double-buffered scores (fmha_tc_ws_kernel), which therefore stays the default; this one is
+// selected with impl = 4.
 //
 // Every mbarrier completes once per use; each role keeps its own running use count, so phases carry across items
 // and nothing is re-initialised between them.  Items are dealt to the CTAs in groups of a few (batch, head) pairs
@@ -32,7 +48,7 @@ namespace dgpt {
 namespace tc {
 
 constexpr int kPpThreads = 384;  // three warpgroups: softmax of tile 0, softmax of tile 1, and (issuer, loader, two idle warps)
-constexpr int kPpSoftmaxRegs = 216, kPpHelperRegs = 56;  // registers per thread after the warpgroups trade them
+constexpr int kPpSoftmaxRegs = 216, kPpHelperRegs = 72;  // registers per thread after the warpgroups trade them
 
 // Packed pairs of fp32 (sm_100 executes fma / add on two lanes of a 64-bit register in one issue slot).
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -53,12 +69,90 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
+// 2^x for two values on the FMA and integer pipes: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic
+// (relative error 1.1e-4, a twentieth of a bf16 step), 2^n by adding n to the exponent bits.  x is clamped at -126,
+// which also turns -inf (a masked score) into a probability of 2^-126 ~ 0.
+constexpr int kPolyPhase = 3;  // which pair of every four takes this route (4 or more: none)
+__device__ __forceinline__ void exp2_pair_fma(float x0, float x1, float& p0, float& p1) {
+  const float kMagic = 12582912.f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+  const uint64_t x2 = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t r2 = add2(x2, pack2(kMagic, kMagic));
+  const uint64_t n2 = add2(r2, pack2(-kMagic, -kMagic));
+  const uint64_t f2 = fma2(n2, pack2(-1.f, -1.f), x2);
+  uint64_t q2 = fma2(pack2(0.05459817f, 0.05459817f), f2, pack2(0.24221788f, 0.24221788f));
+  q2 = fma2(q2, f2, pack2(0.69336749f, 0.69336749f));
+  q2 = fma2(q2, f2, pack2(1.f, 1.f));
+  float r0, r1, q0, q1;
+  unpack2(r2, r0, r1);
+  unpack2(q2, q0, q1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
 constexpr uint32_t kPpTmemCols = 512;
+
+// Eight (four) tcgen05.mma of one product in a single asm statement: the issuing lane shares its scheduler with two
+// busy softmax warps, so every instruction it does not execute is time the tensor pipe does not wait for.  The
+// descriptors advance by constants (in 16-byte units), the first MMA takes the accumulate flag, the others accumulate.
+// S = Q K^T over head_dim: k-step ks reads bytes 32 (ks & 3) of 128-byte row block ks >> 2 (sub = bytes of a block >> 4).
+template <int STEPS>
+__device__ __forceinline__ void umma_ss_chain(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sub) {
+  static_assert(STEPS == 4 || STEPS == 8, "head_dim 64 or 128");
+  if constexpr (STEPS == 8) {
+    asm volatile(
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a, b, s;\n\t"
+        "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\tcvt.u64.u32 s, %4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+        "add.u64 a, %1, 2;\n\tadd.u64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, %1, 4;\n\tadd.u64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, %1, 6;\n\tadd.u64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, %1, s;\n\tadd.u64 b, %2, s;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, a, 2;\n\tadd.u64 b, b, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, a, 2;\n\tadd.u64 b, b, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, a, 2;\n\tadd.u64 b, b, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sub)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a, b;\n\t"
+        "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+        "add.u64 a, %1, 2;\n\tadd.u64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, %1, 4;\n\tadd.u64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, %1, 6;\n\tadd.u64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sub)
+        : "memory");
+  }
+}
+// O (+)= P V over 16 STEPS keys: k-step ks reads 8 TMEM columns of packed P and 16 rows (2048 bytes = 128 units) of V.
+template <int STEPS>
+__device__ __forceinline__ void umma_ts_chain(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  static_assert(STEPS == 4 || STEPS == 8, "64 or 128 keys");
+  asm volatile(
+      "{\n\t.reg .pred p0, pt;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+      "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+      "add.u32 a, %1, 8;\n\tadd.u64 b, %2, 128;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 16;\n\tadd.u64 b, %2, 256;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 24;\n\tadd.u64 b, %2, 384;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+  if constexpr (STEPS == 8) {
+    asm volatile(
+        "{\n\t.reg .pred pt;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "add.u32 a, %1, 32;\n\tadd.u64 b, %2, 512;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 40;\n\tadd.u64 b, %2, 640;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 48;\n\tadd.u64 b, %2, 768;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 56;\n\tadd.u64 b, %2, 896;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
+        : "memory");
+  }
+}
 
 // Which item a CTA works on next.  Groups of `group_bh` (batch, head) pairs; inside a group the items (pair of
 // query tiles x (batch, head)) are ordered longest first and dealt to the CTAs round by round, every other round
@@ -112,7 +206,7 @@ __device__ __forceinline__ PpItem pp_item(const TcParams& p, int bh, int pair) {
   return it;
 }
 
-template <int D>
+template <int D, int PARTS>
 __global__ void __launch_bounds__(kPpThreads, 1)
 fmha_tc_pp_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                   const __grid_constant__ CUtensorMap mv, const TcParams p) {
@@ -132,7 +226,11 @@ fmha_tc_pp_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   const uint32_t aQ = smem_u32(smem), aK = aQ + 2 * kTileBytes, aV = aQ + (2 + KS) * kTileBytes;
   const uint32_t bar0 = smem_u32(bars);
   // barrier indices
-  constexpr int iQ = 0, iQF = 2, iS = 4, iP = 6, iO = 8, iK = 10, iKF = iK + KS, iV = iKF + KS, iVF = iV + VS, nBars = iVF + VS;
+  // Q_t full / free; S_t^h ready (index 2 t + h); P_t^h written (128 arrivals); last product of an item into O_t done;
+  // any product into O_t done; then the K and V rings (full, free)
+  constexpr int iQ = 0, iQF = 2, iS = 4, iP = 8, iO = 12, iPV = 14, iK = 16, iKF = iK + KS, iV = iKF + KS, iVF = iV + VS,
+                nBars = iVF + VS;
+  constexpr int kHN = kBN / PARTS;  // keys per part of a tile (the softmax hands its probabilities over part by part)
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + nBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -141,7 +239,7 @@ fmha_tc_pp_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   const int pt = p.page_tokens;
   if (tid == 0) {
     *abort_flag = 0;
-    for (int i = 0; i < nBars; ++i) mbar_init(bar(i), (i == iP || i == iP + 1) ? kBM : 1);
+    for (int i = 0; i < nBars; ++i) mbar_init(bar(i), (i >= iP && i < iP + 4) ? kBM : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_async_smem();
   }
@@ -236,41 +334,43 @@ fmha_tc_pp_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     // ================= MMA issuer =================
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kPpHelperRegs));
     if ((tid & 31) == 0) {
-      unsigned qn[2] = {0u, 0u}, pn[2] = {0u, 0u}, kn = 0u, vn = 0u;  // uses so far: Q_t, P_t, K ring, V ring
+      unsigned qn[2] = {0u, 0u}, pn[4] = {0u, 0u, 0u, 0u}, kn = 0u, vn = 0u;  // uses so far: Q_t, P_t^h, K ring, V ring
       bool ok = true;
       while (ok && sched.next(bh, pair)) {
         const PpItem it = pp_item(p, bh, pair);
         if (it.nmax == 0) continue;
+        // Descriptors differ only in their 14-bit address field (bytes >> 4), so each product's descriptors are one
+        // 64-bit add away from a base built once per item; the issuing lane has no time for more.
+        const uint64_t dQK = smem_desc(0, 16, 1024), dV = smem_desc(0, kSubBytes, 1024);
         auto issue_s = [&](int t, int j, unsigned kslot) {  // S_t = Q_t K_j^T
           tc_fence_after();
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = (uint32_t)(ks >> 2) * kSubBytes + (uint32_t)(ks & 3) * 32u;
-            umma_ss(tmem + t * 128, smem_desc(aQ + t * kTileBytes + off, 16, 1024),
-                    smem_desc(aK + kslot * kTileBytes + off, 16, 1024), kIdescS, ks > 0 ? 1u : 0u);
-          }
+          umma_ss_chain<D / 16>(tmem + t * 128, dQK + ((aQ + t * kTileBytes) >> 4), dQK + ((aK + kslot * kTileBytes) >> 4),
+                                kIdescS, kSubBytes >> 4);
           umma_commit(bar(iS + t));
           if (j == it.n[t] - 1) umma_commit(bar(iQF + t));  // Q_t may be overwritten by the next item's
         };
-        auto issue_pv = [&](int t, int j, unsigned vslot) {  // O_t (+)= P_t V_j
+        auto issue_pv = [&](int t, int h, int j, unsigned vslot) {  // O_t (+)= P_t^h V_j[64 h .. 64 h + 64)
           tc_fence_after();
-#pragma unroll
-          for (int ks = 0; ks < kBN / 16; ++ks)
-            umma_ts(tmem + kOCol + t * 128, tmem + t * 128 + ks * 8,
-                    smem_desc(aV + vslot * kTileBytes + ks * 2048, kSubBytes, 1024), kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
-          if (j == it.n[t] - 1) umma_commit(bar(iO + t));
+          umma_ts_chain<kHN / 16>(tmem + kOCol + t * 128, tmem + t * 128 + h * (kHN / 2),
+                         dV + ((aV + vslot * kTileBytes + (uint32_t)h * (kHN / 16) * 2048u) >> 4), kIdescPV,
+                         (j > 0 || h > 0) ? 1u : 0u);
+          umma_commit(bar(iPV + t));
+          if (h == PARTS - 1 && j == it.n[t] - 1) umma_commit(bar(iO + t));
         };
-        // first key tile: both score products
+        // first key tile: the four score products
         {
           const unsigned ks = kn % KS;
           ok = wait_or_abort(bar(iK + ks), (kn / KS) & 1u, abort_flag, 43);
-          for (int t = 0; t < 2 && ok; ++t) {
-            if (it.n[t] == 0) continue;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (!ok || it.n[t] == 0) continue;
             ok = wait_or_abort(bar(iQ + t), qn[t] & 1u, abort_flag, 44);
             ++qn[t];
-            if (ok) issue_s(t, 0, ks);
           }
           if (!ok) break;
+#pragma unroll
+          for (int t = 0; t < 2; ++t)
+            if (it.n[t] > 0) issue_s(t, 0, ks);
           umma_commit(bar(iKF + ks));
           ++kn;
         }
@@ -279,22 +379,24 @@ fmha_tc_pp_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           const bool more = j + 1 < it.nmax;
           const unsigned ks = kn % KS;
           ok = wait_or_abort(bar(iV + vs), (vn / VS) & 1u, abort_flag, 45);
-          if (ok && j < it.n[0]) {
-            ok = wait_or_abort(bar(iP + 0), pn[0] & 1u, abort_flag, 46);
-            ++pn[0];
-            if (ok) issue_pv(0, j, vs);
-          }
           if (ok && more) ok = wait_or_abort(bar(iK + ks), (kn / KS) & 1u, abort_flag, 47);
-          if (ok && j + 1 < it.n[0]) issue_s(0, j + 1, ks);
-          if (ok && j < it.n[1]) {
-            ok = wait_or_abort(bar(iP + 1), pn[1] & 1u, abort_flag, 48);
-            ++pn[1];
-            if (ok) issue_pv(1, j, vs);
+#pragma unroll
+          for (int h = 0; h < PARTS; ++h) {
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              if (ok && j < it.n[t]) {
+                ok = wait_or_abort(bar(iP + 2 * t + h), pn[2 * t + h] & 1u, abort_flag, 46);
+                ++pn[2 * t + h];
+              }
+              if (ok && j < it.n[t]) {
+                issue_pv(t, h, j, vs);
+              }
+              if (ok && h == PARTS - 1 && j + 1 < it.n[t]) issue_s(t, j + 1, ks);
+            }
           }
           if (!ok) break;
           umma_commit(bar(iVF + vs));
           ++vn;
-          if (j + 1 < it.n[1]) issue_s(1, j + 1, ks);
           if (more) {
             umma_commit(bar(iKF + ks));
             ++kn;
@@ -313,98 +415,142 @@ fmha_tc_pp_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     const int row = quarter * 32 + (tid & 31);
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     const uint32_t s_addr = lane_addr + t * 128, o_addr = lane_addr + kOCol + t * 128;
-    unsigned sn = 0u, on = 0u, vn = 0u;  // S_t tiles consumed, items finished, V tiles of all items so far
+    unsigned sn[2] = {0u, 0u}, on = 0u, vn = 0u, pvn = 0u;  // S_t^h consumed, items finished, V tiles so far, arrivals (= products into O_t)
     bool fail = false;
+    const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2);
     while (!fail && sched.next(bh, pair)) {
       const PpItem it = pp_item(p, bh, pair);
       const int nt = it.n[t];
       const int q0 = it.q0 + t * kBM;
       const int qi = q0 + row;
       const bool row_ok = qi < p.Tq;
+      const int last_key = p.causal ? min(it.klen - 1, p.q_offset + qi) : it.klen - 1;
       float m = -INFINITY, l = 0.f;
-      for (int j = 0; j < nt; ++j) {
-        const int t0 = j * kBN;
-        // exits are taken by whole warps (the vote makes the decision uniform), never by single lanes
-        if (!__all_sync(0xffffffffu, wait_or_abort(bar(iS + t), sn & 1u, abort_flag, 49))) {
-          fail = true;
-          break;
-        }
-        ++sn;
-        tc_fence_after();
-        const int valid_rows = it.klen - t0;
-        if (valid_rows < kBN) {  // last, partial key tile: value rows past the end may hold anything; clear them so 0 * x stays 0
-          const unsigned vj = vn + (unsigned)j;
-          if (!__all_sync(0xffffffffu, wait_or_abort(bar(iV + (int)(vj % VS)), (vj / VS) & 1u, abort_flag, 50))) {
-            fail = true;
-            break;
-          }
-          if (row >= valid_rows) {
+      for (int j = 0; j < nt && !fail; ++j) {
 #pragma unroll
-            for (int s = 0; s < kSub; ++s) {
-              uint4* vrow = reinterpret_cast<uint4*>(sV + (vj % VS) * kTileBytes + s * kSubBytes + row * 128);
-#pragma unroll
-              for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+        for (int h = 0; h < PARTS; ++h) {
+          const int t0 = j * kBN + h * kHN;
+          // exits are taken by whole warps (the vote makes the decision uniform), never by single lanes
+          if (h == 0) {
+            if (!__all_sync(0xffffffffu, wait_or_abort(bar(iS + t), sn[0] & 1u, abort_flag, 49))) {
+              fail = true;
+              break;
             }
-            fence_async_smem();
+            ++sn[0];
+            tc_fence_after();
           }
-        }
-        const bool need_mask = (t0 + kBN > it.klen) || (p.causal && t0 + kBN - 1 > p.q_offset + q0);
-        const int last_key = p.causal ? min(it.klen - 1, p.q_offset + qi) : it.klen - 1;
-        float sv[kBN];
+          if (h == 0 && it.klen - j * kBN < kBN) {
+            // last, partial key tile: value rows past the end may hold anything; clear them so that 0 * x stays 0
+            const unsigned vj = vn + (unsigned)j;
+            if (!__all_sync(0xffffffffu, wait_or_abort(bar(iV + (int)(vj % VS)), (vj / VS) & 1u, abort_flag, 50))) {
+              fail = true;
+              break;
+            }
+            if (row >= it.klen - j * kBN) {
 #pragma unroll
-        for (int c = 0; c < kBN / 32; ++c) tmem_ld32_nowait(s_addr + c * 32, &sv[c * 32]);
-        tc_wait_ld();
-        if (need_mask) {
+              for (int s = 0; s < kSub; ++s) {
+                uint4* vrow = reinterpret_cast<uint4*>(sV + (vj % VS) * kTileBytes + s * kSubBytes + row * 128);
 #pragma unroll
-          for (int i = 0; i < kBN; ++i) sv[i] = (t0 + i <= last_key) ? sv[i] : -INFINITY;
-        }
-        float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-        for (int i = 0; i < kBN; i += 8) {  // three-input maxima, four independent chains
-#pragma unroll
-          for (int c = 0; c < 4; ++c) mxs[c] = max3(mxs[c], sv[i + 2 * c], sv[i + 2 * c + 1]);
-        }
-        const float mx2 = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * p.scale_log2;
-        float alpha = 1.f;  // lazy rescale: the running maximum only moves when exceeded by 2^8
-        if (mx2 > m + 8.f || m == -INFINITY) {
-          alpha = (m == -INFINITY) ? 0.f : ex2(m - mx2);
-          m = mx2;
-        }
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-          // S_t of this tile was issued behind the P_t V product of the previous one, so O_t is at rest now
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            float v[32];
-            tmem_ld32(o_addr + c * 32, v);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= alpha;
-            tmem_st32(o_addr + c * 32, v);
+                for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+              }
+              fence_async_smem();
+            }
           }
-        }
-        const float m_use = (m == -INFINITY) ? 0.f : m;
-        const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
-        uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};  // four packed partial sums (bit pattern of 0.f, 0.f)
+          const bool need_mask = (t0 + kHN > it.klen) || (p.causal && t0 + kHN - 1 > p.q_offset + q0);
+          float sv[kHN];
 #pragma unroll
-        for (int c = 0; c < kBN / 32; ++c) {
-          uint32_t packed[16];
+          for (int c = 0; c < kHN / 32; ++c) tmem_ld32_nowait(s_addr + h * kHN + c * 32, &sv[c * 32]);
+          tc_wait_ld();
+          if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float x0, x1;
-            unpack2(fma2(pack2(sv[c * 32 + i], sv[c * 32 + i + 1]), scale2, negm2), x0, x1);
-            const float p0 = ex2(x0), p1 = ex2(x1);  // -inf -> 0
-            rs2[(i >> 1) & 3] = add2(rs2[(i >> 1) & 3], pack2(p0, p1));
-            const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+            for (int i = 0; i < kHN; ++i) sv[i] = (t0 + i <= last_key) ? sv[i] : -INFINITY;
           }
-          tmem_st16(s_addr + c * 16, packed);  // P over the scores it came from (they are in registers now)
+          // One sweep turns the scores into probabilities against a given reference maximum `ref` (log2 domain),
+          // writes them as packed bf16 over the scores, and returns their sum and the largest exponent met.
+          auto sweep = [&](float ref, float& sum, float& top) {
+            const uint64_t negm2 = pack2(-ref, -ref);
+            uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};  // four packed partial sums (bit pattern of 0.f, 0.f)
+            float tops[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < kHN / 32; ++c) {
+              uint32_t packed[16];
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const uint64_t x2 = fma2(pack2(sv[c * 32 + i], sv[c * 32 + i + 1]), scale2, negm2);
+                float x0, x1, p0, p1;
+                unpack2(x2, x0, x1);
+                tops[(i >> 1) & 3] = max3(tops[(i >> 1) & 3], x0, x1);
+                if (((i >> 1) & 3) == kPolyPhase) {
+                  exp2_pair_fma(x0, x1, p0, p1);  // one pair in four on the FMA pipe, to take load off the exp2 unit
+                } else {
+                  p0 = ex2(x0);  // -inf -> 0
+                  p1 = ex2(x1);
+                }
+                rs2[(i >> 1) & 3] = add2(rs2[(i >> 1) & 3], pack2(p0, p1));
+                const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+              }
+              // part h goes to columns [32 h, 32 h + 32): over scores that are in registers by now, so the probabilities
+              // of the whole tile are one contiguous A operand and a later part's scores stay untouched
+              tmem_st16(s_addr + h * (kHN / 2) + c * 16, packed);
+            }
+            float ra, rb, rc, rd;
+            unpack2(add2(rs2[0], rs2[1]), ra, rb);
+            unpack2(add2(rs2[2], rs2[3]), rc, rd);
+            sum = (ra + rb) + (rc + rd);
+            top = fmaxf(fmaxf(tops[0], tops[1]), fmaxf(tops[2], tops[3]));
+          };
+          // From the second tile on the running maximum is almost always still good (it only has to be within 2^8 of
+          // the true one), so the probabilities are taken against it at once and the tile's own maximum is found in the
+          // same sweep; only if a score turned out more than 2^8 above it is the tile redone the careful way.
+          bool settled = false;
+          float alpha = 1.f;
+          if (__all_sync(0xffffffffu, m != -INFINITY)) {
+            float sum, top;
+            sweep(m, sum, top);
+            if (!__any_sync(0xffffffffu, top > 8.f)) {
+              l += sum;
+              settled = true;
+            }
+          }
+          if (!settled) {
+            float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < kHN; i += 8) {  // three-input maxima, four independent chains
+#pragma unroll
+              for (int c = 0; c < 4; ++c) mxs[c] = max3(mxs[c], sv[i + 2 * c], sv[i + 2 * c + 1]);
+            }
+            const float mx2 = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * p.scale_log2;
+            if (mx2 > m + 8.f || m == -INFINITY) {  // lazy rescale: the running maximum only moves when exceeded by 2^8
+              alpha = (m == -INFINITY) ? 0.f : ex2(m - mx2);
+              m = mx2;
+            }
+            if ((j > 0 || h > 0) && __any_sync(0xffffffffu, alpha != 1.f)) {
+              // O_t may only be touched when no product into it is in flight: the one this row last arrived for must be
+              // done (the one before it is, or these scores could not have been produced)
+              if (!__all_sync(0xffffffffu, wait_or_abort(bar(iPV + t), (pvn - 1) & 1u, abort_flag, 52))) {
+                fail = true;
+                break;
+              }
+              tc_fence_after();
+#pragma unroll
+              for (int c = 0; c < D / 32; ++c) {
+                float v[32];
+                tmem_ld32(o_addr + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] *= alpha;
+                tmem_st32(o_addr + c * 32, v);
+              }
+            }
+            float sum, top;
+            sweep((m == -INFINITY) ? 0.f : m, sum, top);
+            l = l * alpha + sum;
+          }
+          tc_wait_st();
+          tc_fence_before();
+          mbar_arrive(bar(iP + 2 * t + h));
+          ++pvn;
         }
-        float ra, rb, rc, rd;
-        unpack2(add2(rs2[0], rs2[1]), ra, rb);
-        unpack2(add2(rs2[2], rs2[3]), rc, rd);
-        l = l * alpha + ((ra + rb) + (rc + rd));
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(bar(iP + t));
       }
       vn += (unsigned)it.nmax;
       if (fail) break;
@@ -419,7 +565,7 @@ fmha_tc_pp_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       }
       if (q0 < p.Tq) {  // warp-uniform; tcgen05.ld is warp-collective: every lane reads, only rows that exist are stored
         const float inv = (l > 0.f && nt > 0) ? 1.f / l : 0.f;
-        const long long off = (long long)it.b * p.o_bs + (long long)qi * p.o_rs + (long long)it.h * D;
+        const long long off = (long long)it.b * p.o_bs + (long long)qi * p.o_rs + (long long)it.h * p.d_head;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           float v[32];
@@ -429,7 +575,7 @@ fmha_tc_pp_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0.f;
           }
-          if (row_ok) {
+          if (row_ok && c * 32 < p.d_head) {
             if (p.o_f32) {
               float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.o) + off + c * 32);
 #pragma unroll
@@ -458,7 +604,7 @@ fmha_tc_pp_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 
 int fmha_tc_pp_launch(const FmhaArgs& a, const TcMaps& maps, TcParams p, long long kv_span, cudaStream_t st) {
   using namespace tc;
-  const int D = a.D;
+  const int D = a.D == 32 ? 64 : a.D;  // head_dim 32 rides on the 64-wide kernel (zero-filled boxes)
   const int n_pairs = (a.Tq + 2 * kBM - 1) / (2 * kBM);
   p.BH = a.B * a.H;
   // (batch, head) pairs worked on together: their K and V (2 x span x D bf16 each) should stay in L2 (about 48 MB of it)
@@ -477,13 +623,14 @@ int fmha_tc_pp_launch(const FmhaArgs& a, const TcMaps& maps, TcParams p, long lo
   const int KS = D == 128 ? 3 : 4, VS = D == 128 ? 2 : 4;
   const size_t smem = (size_t)(2 + KS + VS) * (D / 64) * kBN * 128 + 512 + 1024;  // tiles, barriers, alignment slack
   cudaError_t e;
-  if (D == 64) {
-    e = cudaFuncSetAttribute(fmha_tc_pp_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) fmha_tc_pp_kernel<64><<<n_cta, kPpThreads, smem, st>>>(maps.q, maps.k, maps.v, p);
-  } else {
-    e = cudaFuncSetAttribute(fmha_tc_pp_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) fmha_tc_pp_kernel<128><<<n_cta, kPpThreads, smem, st>>>(maps.q, maps.k, maps.v, p);
-  }
+  auto go = [&](auto kernel) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err == cudaSuccess) kernel<<<n_cta, kPpThreads, smem, st>>>(maps.q, maps.k, maps.v, p);
+    return err;
+  };
+  // PARTS = 2 (probabilities handed over in halves of 64 keys so that the first half of P V starts early) measured
+  // slower: 630 / 713 / 722 TFLOP/s on the shapes above - two more barrier round trips per key tile
+  e = D == 64 ? go(fmha_tc_pp_kernel<64, 1>) : go(fmha_tc_pp_kernel<128, 1>);
   if (e != cudaSuccess) {
     set_error("fmha_tc: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     return DGPT_E_CUDA;

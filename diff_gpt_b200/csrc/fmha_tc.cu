@@ -274,7 +274,7 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
     const int qi = q0 + tid;
     const bool row_ok = qi < p.Tq;
     const float inv = (l > 0.f && n_tiles > 0) ? 1.f / l : 0.f;
-    const long long off = (long long)b * p.o_bs + (long long)qi * p.o_rs + (long long)h * D;
+    const long long off = (long long)b * p.o_bs + (long long)qi * p.o_rs + (long long)h * p.d_head;
 #pragma unroll
     for (int c = 0; c < D / 32; ++c) {
       float v[32];
@@ -284,7 +284,7 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0.f;
       }
-      if (row_ok) {
+      if (row_ok && c * 32 < p.d_head) {
         if (p.o_f32) {
           float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.o) + off + c * 32);
 #pragma unroll
@@ -678,7 +678,7 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
       const int qi = q0 + row;
       const bool row_ok = qi < p.Tq;
       const float inv = (l > 0.f && n_tiles > 0) ? 1.f / l : 0.f;
-      const long long off = (long long)b * p.o_bs + (long long)qi * p.o_rs + (long long)h * D + half * (D / 2);
+      const long long off = (long long)b * p.o_bs + (long long)qi * p.o_rs + (long long)h * p.d_head + half * (D / 2);
 #pragma unroll
       for (int c = 0; c < D / 64; ++c) {
         float v[32];
@@ -688,7 +688,7 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0.f;
         }
-        if (row_ok) {
+        if (row_ok && half * (D / 2) + c * 32 < p.d_head) {
           if (p.o_f32) {
             float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.o) + off + c * 32);
 #pragma unroll
@@ -716,7 +716,7 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 }  // namespace tc
 
 bool fmha_tc_supported(const FmhaArgs& a, const dgpt_kv_layout& kv) {
-  if (a.dtype != DGPT_BF16 || (a.D != 64 && a.D != 128)) return false;
+  if (a.dtype != DGPT_BF16 || (a.D != 32 && a.D != 64 && a.D != 128)) return false;
   const int pt = kv.page_tokens;
   if (!((pt >= tc::kBN && pt % tc::kBN == 0) || (pt >= 8 && pt < tc::kBN && tc::kBN % pt == 0))) return false;
   if (kv.page_table == nullptr && pt < tc::kBN) return false;
@@ -729,21 +729,24 @@ bool fmha_tc_supported(const FmhaArgs& a, const dgpt_kv_layout& kv) {
 
 int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
   using namespace tc;
-  const int D = a.D;
+  // head_dim 32 runs on the 64-wide kernels: the boxes stay 64 elements wide, the tensor is 32 wide, and the TMA
+  // engine fills what lies outside the tensor with zeros - Q K^T and P V see zero columns and are unchanged
+  const int d_head = a.D;
+  const int D = d_head == 32 ? 64 : d_head;
   TcMaps maps;
   CUtensorMap &mq = maps.q, &mk = maps.k, &mv = maps.v;
   {
-    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)a.H, (cuuint64_t)a.Tq, (cuuint64_t)a.B};
+    const cuuint64_t dims[4] = {(cuuint64_t)d_head, (cuuint64_t)a.H, (cuuint64_t)a.Tq, (cuuint64_t)a.B};
     const cuuint64_t q_bs = a.q_bs > 0 ? (cuuint64_t)a.q_bs : (cuuint64_t)a.q_rs * a.Tq;
-    const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)a.q_rs * 2, q_bs * 2};
+    const cuuint64_t strides[3] = {(cuuint64_t)d_head * 2, (cuuint64_t)a.q_rs * 2, q_bs * 2};
     const cuuint32_t box[4] = {64, 1, (cuuint32_t)kBM, 1};
     if (!encode_map(&mq, a.q, dims, strides, box)) return DGPT_E_CUDA;
   }
   {
     const int pt = kv.page_tokens;
     cuuint64_t n_pages = kv.page_table ? (kv.n_pages > 0 ? (cuuint64_t)kv.n_pages : (cuuint64_t)1 << 24) : (cuuint64_t)a.B;
-    const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)pt, (cuuint64_t)a.H, n_pages};
-    const cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)kv.head_stride * 2, (cuuint64_t)kv.page_stride * 2};
+    const cuuint64_t dims[4] = {(cuuint64_t)d_head, (cuuint64_t)pt, (cuuint64_t)a.H, n_pages};
+    const cuuint64_t strides[3] = {(cuuint64_t)d_head * 2, (cuuint64_t)kv.head_stride * 2, (cuuint64_t)kv.page_stride * 2};
     const cuuint32_t box[4] = {64, (cuuint32_t)(pt < kBN ? pt : kBN), 1, 1};
     if (!encode_map(&mk, kv.k_base, dims, strides, box)) return DGPT_E_CUDA;
     if (!encode_map(&mv, kv.v_base, dims, strides, box)) return DGPT_E_CUDA;
@@ -763,7 +766,8 @@ int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
   p.Tq = a.Tq;
   p.q_offset = a.q_offset;
   p.causal = a.causal;
-  p.scale_log2 = kLog2e / sqrtf((float)D);
+  p.scale_log2 = kLog2e / sqrtf((float)d_head);
+  p.d_head = d_head;
   p.status = a.status;
   p.n_qt = (a.Tq + kBM - 1) / kBM;
   p.n_work = p.n_qt * a.H * a.B;

@@ -121,7 +121,8 @@ int dgpt_rope_qknorm_kvappend(const void* q, const void* k, const void* v, int64
  * impl: 0 = choose (bf16 with D = 64 or 128 runs on the tcgen05 tensor cores, everything else takes
  * the warp-level online-softmax kernel; of the two tensor-core kernels the warp-specialised one is taken
  * from 4096 keys on, the two-CTAs-per-SM one below), 1 = warp-level kernel, 2 = warp-specialised
- * tensor-core kernel or fail, 3 = tensor-core kernel with two CTAs per SM or fail.
+ * tensor-core kernel or fail, 3 = tensor-core kernel with two CTAs per SM or fail, 4 = persistent tensor-core kernel
+ * with two query tiles per CTA or fail.
  * max_ctas: 0, or a cap on the CTAs of the two-CTAs-per-SM kernel, which then loop over the query tiles - for a
  * caller that runs the kernel on a second stream and wants it to stay on part of the GPU (ignored elsewhere).
  * status: device int32, set non-zero if a bounded wait inside the tensor-core kernel ran out. */

@@ -32,6 +32,28 @@ def test_config2_shape_batched_forward_bf16_head_dim_32():
     assert (got - want).abs().max().item() <= 2e-2 * want.abs().max().item()
 
 
+def test_config2_full_shape_on_the_tensor_core_attention():
+    """Config 2 as BASELINE states it (V512 C256 H8 of 32, L4, bf16, N(0, 0.02) seed 2; 256 sequences x 512 tokens):
+    head_dim 32 takes the tensor-core attention kernel; sequences do not interact, so four of the 256 rows of the
+    full-batch result are compared with the oracle's forward of those four sequences."""
+    from diff_gpt_b200 import _lib
+
+    shape = ref_math.Shape(vocab_size=512, n_embd=256, n_head=8, n_layer=4, block_size=512)
+    w = ref_math.random_weights(shape, seed=2, dtype=torch.bfloat16)
+    idx = torch.randint(0, 512, (256, 512), generator=torch.Generator().manual_seed(2))
+    rows = [0, 77, 130, 255]
+    want = ref_math.forward(shape, w, idx[rows]).float()
+    model = _gpu_model(shape, w, torch.bfloat16)
+    timer = _lib.KernelTimer()
+    with _lib.timed(timer):
+        got = model(idx.cuda())[0]
+    torch.cuda.synchronize()
+    assert got.shape == (256, 512, 512)
+    err = (got[rows].float().cpu() - want).abs().max().item() / want.abs().max().item()
+    assert err <= 2e-2, err
+    assert timer.summary()["dgpt_fmha_prefill"]["launches"] == 4
+
+
 def test_config3_shape_many_series_one_trajectory_teacher_forced():
     """Config 3 narrowed: 5 series x 1 trajectory, 7 channels of which 2 are forced from a schedule, head_dim 64.
     One trajectory per series takes the per-row path with the prompt split along the keys (no shared-prompt phase).
