@@ -82,9 +82,16 @@ PROTOTYPES = {
         [_p, _i64, _i32, _i32, _f32, _f32, _f32, _u64, _i64, _p, _i32, _p, _p, _i32, _i64, _p, _p, _p, _p, _i64, _i32, _p],
     ),
     "dgpt_nucleus_filter": (C.c_int, [_p, _i64, _p, _i64, _i32, _i32, _f32, _i32, _p]),
+    "dgpt_lmhead_workspace_bytes": (_sz, [_i32]),
+    "dgpt_lmhead_sample": (
+        C.c_int,
+        [_p, _i64, _p, _i64, _f32, _f32, _f32, _u64, _i64, _p, _i32, _p, _p, _i32, _i64, _p, _p, _p, _p, _i64, _p, _i64, _p,
+         _sz, _i32, _i32, _i32, _i32, _p, _p],
+    ),
 }
 _NOT_LAUNCHING = {
     "dgpt_last_error", "dgpt_version", "dgpt_decode_attn_workspace_bytes", "dgpt_decode_attn_static_capacity_bytes",
+    "dgpt_lmhead_workspace_bytes",
 }
 
 

@@ -5,6 +5,9 @@
 //   mode 0:  out[m, n]     = bf16(acc[m, n])
 //   mode 1:  out[m, n / 2] = swiglu(bf16(acc[m, n]), bf16(acc[m, n + 1]))   for even n  (interleaved gate / linear)
 //   mode 2:  out[m, n]     = bf16(resid[m, n] + acc[m, n])                    (the residual add of addmm, one rounding)
+//   mode 3:  nothing is stored: row m keeps the best key of  key[m, n] = cap(bf16(acc[m, n])) / T + Gumbel noise(m, n)
+//            (no noise and T = 1 for an arg-max) in best[m], a 64-bit word (order-preserving key bits, ~n) raised with
+//            atomicMax - the tied-embedding head with the draw in its epilogue, so [M, N] logits never reach HBM
 //
 // Persistent, warp-specialised CTAs of 320 threads, one per SM, tiles of 128 x BN outputs (BN = 256, 192 or 128,
 // whichever needs the fewest rounds of tiles over the SMs) taken round robin:
@@ -19,6 +22,8 @@
 // fill 148 SMs evenly and no overlapped epilogue - 30.7 us.
 // Every mbarrier wait is bounded; a wait that runs out raises a CTA-wide abort flag, is reported through
 // the status word, and every role drains what it issued before TMEM is freed.
+#include "linear.cuh"
+#include "sampling.cuh"
 #include "tcgen05.cuh"
 
 namespace dgpt {
@@ -40,7 +45,14 @@ struct GemmParams {
   int M, N, K, mode;
   float alpha, limit;
   int* status;
+  HeadDraw draw;  // mode 3
 };
+
+// order-preserving map of a float onto unsigned integers
+__device__ __forceinline__ uint32_t float_order_bits(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
   asm volatile(
@@ -168,11 +180,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
       tc_fence_after();
       const int row = tm * kGM + (warp & 3) * 32 + lane;
       const int col0 = tn * kGN;
+      float best_v = -INFINITY;  // mode 3: this thread's best key over its columns of the tile, and where
+      int best_n = 0x7fffffff;
+      long long traj = 0;
+      int step = 0;
+      if (p.mode == 3 && row < p.M) {
+        traj = p.draw.traj_ids ? p.draw.traj_ids[row] : p.draw.traj_id0 + row;
+        step = p.draw.step_base + (p.draw.step_ptr ? *p.draw.step_ptr : 0);
+      }
 #pragma unroll 1
       for (int c = c_begin; c < c_begin + kGN / 2; c += 32) {
         float v[32];
         tmem_ld32(lane_addr + a * kAccStride + c, v);  // all lanes load; stores below are predicated
         if (row >= p.M) continue;
+        if (p.mode == 3) {
+          using B = Io<__nv_bfloat16>;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {  // four columns per random-number block
+            const int n0 = col0 + c + 4 * q;
+            if (n0 >= p.N) break;  // N is a multiple of 16
+            uint32_t rnd[4] = {0u, 0u, 0u, 0u};
+            if (p.draw.inv_temperature > 0.f)
+              philox4x32_10_words((uint32_t)traj, (uint32_t)((unsigned long long)traj >> 32), (uint32_t)step,
+                                  0x80000000u | (uint32_t)(n0 >> 2), p.draw.seed_lo, p.draw.seed_hi, rnd);
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              float z = B::round(v[4 * q + x]);  // the logit as a bf16 Linear would have written it
+              if (p.draw.cap > 0.f) z = softcap_value<__nv_bfloat16>(z, p.draw.cap);
+              float key = z;
+              if (p.draw.inv_temperature > 0.f) {
+                const float u = ((float)(rnd[x] >> 8) + 0.5f) * (1.f / 16777216.f);  // in (0, 1)
+                key = z * p.draw.inv_temperature - __logf(-__logf(u));              // arg-max of these keys ~ softmax(z / T)
+              }
+              if (key > best_v) {  // columns are visited in increasing order: the lowest index wins ties
+                best_v = key;
+                best_n = n0 + x;
+              }
+            }
+          }
+          continue;
+        }
         if (p.mode == 0 || p.mode == 2) {
           __nv_bfloat16* dst = p.out + (long long)row * p.out_rs + col0 + c;
 #pragma unroll
@@ -205,6 +252,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
           }
         }
       }
+      if (p.mode == 3 && row < p.M && best_n != 0x7fffffff)
+        atomicMax(p.draw.best + row, ((unsigned long long)float_order_bits(best_v) << 32) | (uint32_t)(~(uint32_t)best_n));
       tc_fence_before();
       mbar_arrive(bar_acce + 8 * a);
     }
@@ -271,20 +320,21 @@ extern "C" int dgpt_bounded_wait_probe(int32_t arrive, int64_t limit_cycles, int
   return launch_status("bounded_wait_probe");
 }
 
-extern "C" int dgpt_linear(const void* a, int64_t a_row_stride, const void* w, int64_t w_row_stride, void* out,
-                           int64_t out_row_stride, const void* resid, int64_t resid_row_stride, int32_t M, int32_t N,
-                           int32_t K, int32_t epilogue, float alpha, float limit, int32_t dtype, int32_t* status,
-                           void* stream) {
-  DGPT_REQUIRE(a && w && out, "linear: NULL pointer");
+int dgpt::linear_launch(const void* a, int64_t a_row_stride, const void* w, int64_t w_row_stride, void* out,
+                        int64_t out_row_stride, const void* resid, int64_t resid_row_stride, int32_t M, int32_t N,
+                        int32_t K, int32_t epilogue, float alpha, float limit, int32_t dtype, int32_t* status,
+                        const HeadDraw* draw, void* stream) {
+  DGPT_REQUIRE(a && w && (out || epilogue == 3), "linear: NULL pointer");
   DGPT_REQUIRE(M >= 0 && N > 0 && K > 0, "linear: bad sizes");
-  DGPT_REQUIRE(epilogue >= 0 && epilogue <= 2, "linear: epilogue must be 0 (store), 1 (SwiGLU of interleaved pairs) or 2 (add)");
+  DGPT_REQUIRE(epilogue >= 0 && epilogue <= 3, "linear: epilogue must be 0 (store), 1 (SwiGLU of interleaved pairs), 2 (add) or 3 (draw)");
   DGPT_REQUIRE(epilogue != 2 || resid, "linear: epilogue 2 needs the matrix to add");
+  DGPT_REQUIRE(epilogue != 3 || (draw && draw->best), "linear: epilogue 3 needs the draw parameters");
   if (dtype != DGPT_BF16) {
     set_error("linear: only bf16 is built (dtype %d)", dtype);
     return DGPT_E_UNSUPPORTED;
   }
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  if (!al(a) || !al(w) || !al(out) || K % 8 != 0 || N % 16 != 0 || a_row_stride % 8 != 0 || w_row_stride % 8 != 0 ||
+  if (!al(a) || !al(w) || (out && !al(out)) || K % 8 != 0 || N % 16 != 0 || a_row_stride % 8 != 0 || w_row_stride % 8 != 0 ||
       out_row_stride % 8 != 0 || (epilogue == 2 && (!al(resid) || resid_row_stride % 8 != 0))) {
     set_error("linear: pointers must be 16-byte aligned, K and the row strides multiples of 8, N a multiple of 16");
     return DGPT_E_UNSUPPORTED;
@@ -337,6 +387,7 @@ extern "C" int dgpt_linear(const void* a, int64_t a_row_stride, const void* w, i
   p.M = M; p.N = N; p.K = K; p.mode = epilogue;
   p.alpha = alpha; p.limit = limit;
   p.status = status;
+  if (draw) p.draw = *draw;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t smem = (size_t)tc::kGStages * (tc::kGABytes + (size_t)bn * 128) + 256 + 1024;
   const int tiles = tiles_m * ((N + bn - 1) / bn);
@@ -345,4 +396,13 @@ extern "C" int dgpt_linear(const void* a, int64_t a_row_stride, const void* w, i
   else if (bn == 192) launch_dep(tc::gemm_tc_kernel<192>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
   else launch_dep(tc::gemm_tc_kernel<128>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
   return launch_status("linear");
+}
+
+extern "C" int dgpt_linear(const void* a, int64_t a_row_stride, const void* w, int64_t w_row_stride, void* out,
+                           int64_t out_row_stride, const void* resid, int64_t resid_row_stride, int32_t M, int32_t N,
+                           int32_t K, int32_t epilogue, float alpha, float limit, int32_t dtype, int32_t* status,
+                           void* stream) {
+  DGPT_REQUIRE(epilogue >= 0 && epilogue <= 2, "linear: epilogue must be 0 (store), 1 (SwiGLU of interleaved pairs) or 2 (add)");
+  return linear_launch(a, a_row_stride, w, w_row_stride, out, out_row_stride, resid, resid_row_stride, M, N, K, epilogue, alpha,
+                       limit, dtype, status, nullptr, stream);
 }

@@ -50,13 +50,13 @@ class DecodeRun:
 
     @staticmethod
     def key_for(model, prompt_lens, num_samples, max_tokens, sampler, seed, has_force, page_tokens, use_graph,
-                fmha_impl, overlap_prefix, shared_prefix=None) -> tuple:
+                fmha_impl, overlap_prefix, shared_prefix=None, fused_head=True) -> tuple:
         spec = (1.0, 1.0) if sampler is None else (sampler.native_spec() if isinstance(sampler, Sampler) else None)
         emb = model.token_embedding_table.weight
         return (
             id(model), str(emb.device), emb.dtype, tuple(prompt_lens), num_samples, max_tokens, spec,
             None if spec is not None else id(sampler), seed, has_force, page_tokens, use_graph, fmha_impl,
-            overlap_prefix, shared_prefix,
+            overlap_prefix, shared_prefix, fused_head,
         )
 
     def __init__(
@@ -76,6 +76,7 @@ class DecodeRun:
         kv_pool: torch.Tensor | None = None,
         overlap_prefix: bool = True,
         shared_prefix: bool | None = None,
+        fused_head: bool = True,
     ) -> None:
         self.model = model
         emb = model.token_embedding_table.weight
@@ -101,7 +102,7 @@ class DecodeRun:
         self.prompt_lens = lens
         self.key = self.key_for(
             model, lens, N, G, sampler, seed, force_schedules is not None, page_tokens, use_graph, fmha_impl,
-            overlap_prefix, shared_prefix,
+            overlap_prefix, shared_prefix, fused_head,
         )
         self.packed = model.packed_weights()  # the graph holds these tensors' addresses
         self.cache = PagedKVCache(L, H, D, S, N, max(lens), G, dt, dev, page_tokens=page_tokens, pool=kv_pool)
@@ -155,7 +156,21 @@ class DecodeRun:
             fmha_impl=fmha_impl,
             overlap_prefix=overlap_prefix and shared,
         )
-        self.plan = ForwardPlan(model, self.R, 1)
+        # The head of a decode step.  With one of the library's samplers and a bf16 model it is one call,
+        # dgpt_lmhead_sample: without a top-p filter the logits are sampled inside the GEMM's epilogue and never
+        # stored (`fused_head`); with one, or when a caller wants to see them, the GEMM writes them for the
+        # sampling kernel.  Other samplers and fp32 models get the logits from the forward plan.
+        C, V = model.n_embd, model.vocab_size
+        self.lmhead = self.native and dt == torch.bfloat16 and C % 8 == 0 and V % 16 == 0
+        nucleus = self.top_p < 1.0 and self.temperature > 0.0
+        self.head_logits = None
+        self.head_ws = None
+        if self.lmhead:
+            if nucleus or not fused_head:
+                self.head_logits = torch.empty((self.R, V), dtype=dt, device=dev)
+            else:
+                self.head_ws = torch.empty(max(1, ops.lmhead_workspace_bytes(self.R) // 8), dtype=torch.int64, device=dev)
+        self.plan = ForwardPlan(model, self.R, 1, want_logits=not self.lmhead)
         self.graph = None
         self.done = 0  # tokens produced so far per row
         self.rng = None
@@ -238,11 +253,23 @@ class DecodeRun:
         self.history[rows, g] = col
 
     # -- stepping ------------------------------------------------------------------------
+    @property
+    def logits(self) -> torch.Tensor | None:
+        """Raw (not yet soft-capped) logits of the last decode step, or None when they were never stored."""
+        return self.head_logits if self.lmhead else self.plan.logits
+
     def _body(self) -> None:
         """One decode step: forward of the current tokens, advance the position, draw the next tokens."""
         logits = self.plan.run(self.tokens, self.bind)
         ops.step_advance(self.step, 1)
-        if self.native:
+        if self.lmhead:
+            ops.lmhead_sample(
+                self.plan.xn, self.packed.emb, self.tokens, cap=self.cap, temperature=self.temperature, top_p=self.top_p,
+                seed=self.seed, traj_ids=self.traj_ids, step=self.step, force_schedule=self.force,
+                force_group_rows=self.N, force_group_stride=self.G if self.force is not None else 0,
+                history_tokens=self.history, logits_out=self.head_logits, workspace=self.head_ws, status=self.plan.status,
+            )
+        elif self.native:
             self._sample(logits, slice(0, self.R), row_stride=logits.stride(0))
 
     def start(self) -> None:
@@ -266,6 +293,12 @@ class DecodeRun:
         if self.use_graph and self.graph is None:
             # warm the forward (cuBLAS handles, lazy module loads) without touching tokens or the counter
             self.plan.run(self.tokens, self.bind)
+            if self.lmhead:  # and the head GEMM (function attributes, tensor-map encoder) into a scratch token buffer
+                ops.lmhead_sample(
+                    self.plan.xn, self.packed.emb, torch.empty_like(self.tokens), cap=self.cap, temperature=self.temperature,
+                    top_p=self.top_p, seed=self.seed, traj_ids=self.traj_ids, step=self.step, logits_out=self.head_logits,
+                    workspace=self.head_ws, status=self.plan.status,
+                )
             ops.step_advance(self.step, 0)
             torch.cuda.synchronize(self.dev)
             self.graph = torch.cuda.CUDAGraph()

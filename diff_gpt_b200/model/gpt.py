@@ -171,6 +171,8 @@ class ForwardPlan:
         self.xn = buf(n_out, C)
         self.last = buf(n_out, C) if (last_only and T > 1) else None
         self.logits = buf(n_out, V) if want_logits else None
+        # the tied-embedding head on the library's tcgen05 GEMM (bf16 with tileable sizes); fp32 stays on cuBLAS
+        self.own_head = dt == torch.bfloat16 and C % 8 == 0 and V % 16 == 0
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         # tcgen05 GEMM + SwiGLU epilogue: bf16 with tileable sizes, and enough rows to fill the tensor cores
         self.fused_ffn = FUSED_FFN and dt == torch.bfloat16 and C % 8 == 0 and n >= FUSED_FFN_MIN_ROWS
@@ -314,8 +316,11 @@ class ForwardPlan:
         ops.depthmix([final], None, None, self.xn)
         if self.logits is None:
             return None
-        with region("gemm_logits"):
-            torch.mm(self.xn, W.emb.t(), out=self.logits)
+        if self.own_head:
+            ops.linear(self.xn, W.emb, self.logits, status=self.status)
+        else:
+            with region("gemm_logits"):
+                torch.mm(self.xn, W.emb.t(), out=self.logits)
         return self.logits
 
 

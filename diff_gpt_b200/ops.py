@@ -470,3 +470,50 @@ def nucleus_filter(logits: torch.Tensor, top_p: float) -> torch.Tensor:
 
 def attn_scale(D: int) -> float:
     return 1.0 / math.sqrt(D)
+
+
+def lmhead_workspace_bytes(R: int) -> int:
+    return int(lib.dgpt_lmhead_workspace_bytes(R))
+
+
+def lmhead_sample(
+    xn: torch.Tensor,
+    emb: torch.Tensor,
+    out_tokens: torch.Tensor,
+    *,
+    cap: float = 0.0,
+    temperature: float = 1.0,
+    top_p: float = 1.0,
+    seed: int = 0,
+    traj_id0: int = 0,
+    traj_ids: torch.Tensor | None = None,
+    step_base: int = 0,
+    step: torch.Tensor | None = None,
+    force_schedule: torch.Tensor | None = None,
+    force_group_rows: int = 1,
+    force_group_stride: int = 0,
+    out_masks: torch.Tensor | None = None,
+    history_tokens: torch.Tensor | None = None,
+    history_masks: torch.Tensor | None = None,
+    logits_out: torch.Tensor | None = None,
+    workspace: torch.Tensor | None = None,
+    status: torch.Tensor | None = None,
+) -> None:
+    """Head GEMM + soft-cap + draw in one call (`dgpt_lmhead_sample`).  With `logits_out`, or a top-p filter, the
+    logits are written and sampled by the sampling kernel; otherwise they never leave the chip (needs `workspace`)."""
+    _cuda(xn, emb, out_tokens, traj_ids, step, force_schedule, out_masks, history_tokens, history_masks, logits_out, workspace, status)
+    R, Cdim = xn.shape
+    V = emb.shape[0]
+    assert emb.shape[1] == Cdim and xn.stride(1) == 1 and emb.stride(1) == 1
+    assert out_tokens.dtype == torch.int32 and out_tokens.numel() >= R
+    hs = 0 if history_tokens is None else history_tokens.stride(0)
+    check(
+        lib.dgpt_lmhead_sample(
+            xn.data_ptr(), xn.stride(0), emb.data_ptr(), emb.stride(0), cap, temperature, top_p,
+            seed & 0xFFFFFFFFFFFFFFFF, traj_id0, _ptr(traj_ids), step_base, _ptr(step), _ptr(force_schedule),
+            force_group_rows, force_group_stride, out_tokens.data_ptr(), _ptr(out_masks), _ptr(history_tokens),
+            _ptr(history_masks), hs, _ptr(logits_out), 0 if logits_out is None else logits_out.stride(0), _ptr(workspace),
+            0 if workspace is None else workspace.numel() * workspace.element_size(), R, Cdim, V, dtype_code(xn),
+            _ptr(status), _stream(),
+        )
+    )

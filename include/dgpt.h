@@ -304,6 +304,30 @@ int dgpt_sample(const void* logits, int64_t logits_row_stride, int32_t R, int32_
                 int32_t force_group_rows, int64_t force_group_stride, int32_t* out_tokens, int32_t* out_masks, int32_t* history_tokens,
                 int32_t* history_masks, int64_t history_stride, int32_t dtype, void* stream);
 
+/* The model's head in one call: tied-embedding logits, soft-cap, and the draw of one token per row with teacher forcing.
+ *   logits[r, v] = sum_c xn[r, c] * emb[v, c]          (xn = the final RMSNorm's output, dgpt_depthmix with one candidate)
+ *   then exactly the rule of dgpt_sample (cap, top-p, temperature, forcing, history).
+ * Replaces the tied nn.Linear and the cap of src/diff_gpt/model/gpt.py:181-186 together with
+ * sampler/temperature.py:21-25, sampler/nucleus.py:29-40 and the sample-or-force step of model/engine.py:106-146.
+ * Two forms, chosen by the arguments:
+ *   - top_p < 1 (with temperature > 0), or logits_out non-NULL: the GEMM (tcgen05) writes bf16 logits [R, V] to
+ *     logits_out, then the sampling kernel reads them; tokens are those of dgpt_linear + dgpt_sample.
+ *   - otherwise the logits are never stored: the GEMM's epilogue soft-caps them, adds Gumbel noise from
+ *     Philox4x32-10 with key = seed and counter = (traj id low, traj id high, step + step_base, 2^31 | token / 4)
+ *     - the arg-max of z / T + noise is a draw from softmax(z / T); no noise for temperature 0 - and keeps each row's
+ *     best (key, token) in `workspace`; ties go to the lower token.  Same distribution as dgpt_sample, another stream.
+ * xn: device [R, C]; emb: device [V, C] (nn.Embedding layout); workspace: device, 8-byte aligned, from
+ * dgpt_lmhead_workspace_bytes (second form only; cleared by the call).  bf16 only; C a multiple of 8, V of 16.
+ * The remaining arguments are those of dgpt_sample.  status: device int32, set non-zero if a bounded wait ran out. */
+size_t dgpt_lmhead_workspace_bytes(int32_t R);
+int dgpt_lmhead_sample(const void* xn, int64_t xn_row_stride, const void* emb, int64_t emb_row_stride, float cap,
+                       float temperature, float top_p, uint64_t seed, int64_t traj_id0, const int64_t* traj_ids,
+                       int32_t step_base, const int32_t* step_ptr, const int32_t* force_schedule,
+                       int32_t force_group_rows, int64_t force_group_stride, int32_t* out_tokens, int32_t* out_masks,
+                       int32_t* history_tokens, int32_t* history_masks, int64_t history_stride, void* logits_out,
+                       int64_t logits_row_stride, void* workspace, size_t workspace_bytes, int32_t R, int32_t C,
+                       int32_t V, int32_t dtype, int32_t* status, void* stream);
+
 /* filtered = logits where the token is in the top-p set (same rule as dgpt_sample, no soft-cap), -inf elsewhere.
  * Lets a top-p filter sit in front of an arbitrary inner sampler.
  * Replaces src/diff_gpt/sampler/nucleus.py:29-39.  logits, filtered: device [R, V] with row strides. */

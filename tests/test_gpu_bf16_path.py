@@ -30,12 +30,13 @@ def _forced_step_logits(model, prompts, n_traj, streams, **kw):
     from diff_gpt_b200.model.engine import DecodeRun
 
     G = len(streams[0])
-    run = DecodeRun(model, prompts, n_traj, G, TemperatureSampler(0.0), 42, [list(s) for s in streams], **kw)
+    # fused_head off: the head GEMM writes the logits (with it on they are sampled in the GEMM's epilogue and never stored)
+    run = DecodeRun(model, prompts, n_traj, G, TemperatureSampler(0.0), 42, [list(s) for s in streams], fused_head=False, **kw)
     run.start()
     got = [_capped(run.logits0).repeat_interleave(n_traj, 0).cpu()]
     for _ in range(G - 1):
         run.advance(1)
-        got.append(_capped(run.plan.logits).cpu())
+        got.append(_capped(run.logits).cpu())
     run.check_status()
     hist = run.history.cpu()[:, :G]
     for s, stream in enumerate(streams):

@@ -131,7 +131,7 @@ def test_config1_teacher_forced_logits_and_argmax_stream():
     got = [15 * torch.tanh(run.logits0[0].float() / 15).cpu().numpy()]
     for _ in range(G - 1):
         run.advance(1)
-        lg = run.plan.logits[0].float()
+        lg = run.logits[0].float()
         got.append((15 * torch.tanh(lg / 15)).cpu().numpy())
     got = np.stack(got)
     assert np.abs(got - ref_logits).max() <= 1e-4 * np.abs(ref_logits).max()
