@@ -486,14 +486,12 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     // ================= MMA issuer (one lane) =================
     if ((tid & 31) == 0 && n_tiles > 0) {
       constexpr int kStepsS = D / 16, kStepsPV = kBN / 16;
+      // The products are issued as one asm statement each (constant descriptor steps): this lane shares its scheduler
+      // with two softmax warps, and every instruction it does not execute is time the tensor pipe does not wait for.
+      const uint64_t dQK = smem_desc(0, 16, 1024), dV = smem_desc(0, kSubBytes, 1024);
       auto issue_s = [&](int buf, int kslot) {  // S(buf) = Q K(kslot)^T
         tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < kStepsS; ++ks) {
-          const uint32_t off = (uint32_t)(ks >> 2) * kSubBytes + (uint32_t)(ks & 3) * 32u;
-          umma_ss(tmem + buf * 128, smem_desc(aQ + off, 16, 1024), smem_desc(aK + kslot * kTileBytes + off, 16, 1024),
-                  kIdescS, ks > 0 ? 1u : 0u);
-        }
+        umma_ss_chain<kStepsS>(tmem + buf * 128, dQK + (aQ >> 4), dQK + ((aK + kslot * kTileBytes) >> 4), kIdescS, kSubBytes >> 4);
         umma_commit(bar_s0 + 8 * buf);
         umma_commit(bar_kf0 + 8 * kslot);
       };
@@ -517,10 +515,7 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         if (ok && next_s) ok = wait_or_abort(bar_k0 + 8 * ((j + 2) % 3), (uint32_t)(((j + 2) / 3) & 1), abort_flag, 22);
         if (!ok) break;
         tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < kStepsPV; ++ks)
-          umma_ts(tmem + kOCol, tmem + kPCol + buf * 64 + ks * 8,
-                  smem_desc(aV + buf * kTileBytes + ks * 2048, kSubBytes, 1024), kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
+        umma_ts_chain<kStepsPV>(tmem + kOCol, tmem + kPCol + buf * 64, dV + ((aV + buf * kTileBytes) >> 4), kIdescPV, j > 0 ? 1u : 0u);
         umma_commit(bar_o0 + 8 * buf);
         last_o[buf] = (int)ph;
         if (next_s) {
@@ -600,16 +595,15 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 #pragma unroll
       for (int c = 0; c < kHalf / 32; ++c) tmem_ld32_nowait(lane_addr + buf * 128 + half * kHalf + c * 32, &sv[c * 32]);
       tc_wait_ld();
-      float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < kHalf; ++i) {
-          sv[i] = (c0 + i <= last_key) ? sv[i] : -INFINITY;
-          mxs[i & 3] = fmaxf(mxs[i & 3], sv[i]);
-        }
-      } else {
+        for (int i = 0; i < kHalf; ++i) sv[i] = (c0 + i <= last_key) ? sv[i] : -INFINITY;
+      }
+      float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < kHalf; ++i) mxs[i & 3] = fmaxf(mxs[i & 3], sv[i]);
+      for (int i = 0; i < kHalf; i += 8) {  // three-input maxima, four independent chains
+#pragma unroll
+        for (int c = 0; c < 4; ++c) mxs[c] = max3(mxs[c], sv[i + 2 * c], sv[i + 2 * c + 1]);
       }
       const float mine = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
       bool xok = true;
@@ -643,21 +637,26 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
         }
       }
       const float m_use = (m == -INFINITY) ? 0.f : m;
-      float rs[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
+      uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};  // four packed partial sums (bit pattern of 0.f, 0.f)
 #pragma unroll
       for (int c = 0; c < kHalf / 32; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2(fmaf(sv[c * 32 + i], p.scale_log2, -m_use));  // -inf -> 0
-          const float p1 = ex2(fmaf(sv[c * 32 + i + 1], p.scale_log2, -m_use));
-          rs[(i >> 1) & 3] += p0 + p1;
+          float x0, x1;
+          unpack2(fma2(pack2(sv[c * 32 + i], sv[c * 32 + i + 1]), scale2, negm2), x0, x1);  // one issue slot for the pair
+          const float p0 = ex2(x0), p1 = ex2(x1);  // -inf -> 0
+          rs2[(i >> 1) & 3] = add2(rs2[(i >> 1) & 3], pack2(p0, p1));
           const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
           packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
         }
         tmem_st16(lane_addr + kPCol + buf * 64 + half * (kHalf / 2) + c * 16, packed);
       }
-      l = l * alpha + ((rs[0] + rs[1]) + (rs[2] + rs[3]));  // sum over this thread's columns only
+      float ra, rb, rc, rd;
+      unpack2(add2(rs2[0], rs2[1]), ra, rb);
+      unpack2(add2(rs2[2], rs2[3]), rc, rd);
+      l = l * alpha + ((ra + rb) + (rc + rd));  // sum over this thread's columns only
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_p0 + 8 * buf);

@@ -191,6 +191,109 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   return false;
 }
 
+// Packed pairs of fp32 (sm_100 executes fma / add on two lanes of a 64-bit register in one issue slot).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// 2^x for two values on the FMA and integer pipes: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic
+// (relative error 1.1e-4, a twentieth of a bf16 step), 2^n by adding n to the exponent bits.  x is clamped at -126,
+// which also turns -inf (a masked score) into a probability of 2^-126 ~ 0.
+constexpr int kPolyPhase = 3;  // which pair of every four takes this route (4 or more: none)
+__device__ __forceinline__ void exp2_pair_fma(float x0, float x1, float& p0, float& p1) {
+  const float kMagic = 12582912.f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+  const uint64_t x2 = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t r2 = add2(x2, pack2(kMagic, kMagic));
+  const uint64_t n2 = add2(r2, pack2(-kMagic, -kMagic));
+  const uint64_t f2 = fma2(n2, pack2(-1.f, -1.f), x2);
+  uint64_t q2 = fma2(pack2(0.05459817f, 0.05459817f), f2, pack2(0.24221788f, 0.24221788f));
+  q2 = fma2(q2, f2, pack2(0.69336749f, 0.69336749f));
+  q2 = fma2(q2, f2, pack2(1.f, 1.f));
+  float r0, r1, q0, q1;
+  unpack2(r2, r0, r1);
+  unpack2(q2, q0, q1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// Eight (four) tcgen05.mma of one product in a single asm statement: the issuing lane shares its scheduler with two
+// busy softmax warps, so every instruction it does not execute is time the tensor pipe does not wait for.  The
+// descriptors advance by constants (in 16-byte units), the first MMA takes the accumulate flag, the others accumulate.
+// S = Q K^T over head_dim: k-step ks reads bytes 32 (ks & 3) of 128-byte row block ks >> 2 (sub = bytes of a block >> 4).
+template <int STEPS>
+__device__ __forceinline__ void umma_ss_chain(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sub) {
+  static_assert(STEPS == 4 || STEPS == 8, "head_dim 64 or 128");
+  if constexpr (STEPS == 8) {
+    asm volatile(
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a, b, s;\n\t"
+        "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\tcvt.u64.u32 s, %4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+        "add.u64 a, %1, 2;\n\tadd.u64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, %1, 4;\n\tadd.u64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, %1, 6;\n\tadd.u64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, %1, s;\n\tadd.u64 b, %2, s;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, a, 2;\n\tadd.u64 b, b, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, a, 2;\n\tadd.u64 b, b, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, a, 2;\n\tadd.u64 b, b, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sub)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred pf, pt;\n\t.reg .b64 a, b;\n\t"
+        "setp.ne.b32 pf, 0, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pf;\n\t"
+        "add.u64 a, %1, 2;\n\tadd.u64 b, %2, 2;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, %1, 4;\n\tadd.u64 b, %2, 4;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t"
+        "add.u64 a, %1, 6;\n\tadd.u64 b, %2, 6;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, pt;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sub)
+        : "memory");
+  }
+}
+// O (+)= P V over 16 STEPS keys: k-step ks reads 8 TMEM columns of packed P and 16 rows (2048 bytes = 128 units) of V.
+template <int STEPS>
+__device__ __forceinline__ void umma_ts_chain(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  static_assert(STEPS == 4 || STEPS == 8, "64 or 128 keys");
+  asm volatile(
+      "{\n\t.reg .pred p0, pt;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+      "setp.ne.b32 p0, %4, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p0;\n\t"
+      "add.u32 a, %1, 8;\n\tadd.u64 b, %2, 128;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 16;\n\tadd.u64 b, %2, 256;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 24;\n\tadd.u64 b, %2, 384;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+  if constexpr (STEPS == 8) {
+    asm volatile(
+        "{\n\t.reg .pred pt;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "add.u32 a, %1, 32;\n\tadd.u64 b, %2, 512;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 40;\n\tadd.u64 b, %2, 640;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 48;\n\tadd.u64 b, %2, 768;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t"
+        "add.u32 a, %1, 56;\n\tadd.u64 b, %2, 896;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, pt;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
+        : "memory");
+  }
+}
+
 constexpr int kBM = 128;  // query rows per MMA (the M of every tcgen05.mma here)
 constexpr int kBN = 128;  // keys per tile
 

@@ -111,6 +111,7 @@ FUSED_FFN_MIN_ROWS = 256
 # (two per SM, the kernel's own residency, leave no registers for the per-row kernel: 1270 against 1250 ms per
 # 255 config-4 steps; caps below ~100 make this phase the longer one), 0 = no cap.
 PREFIX_CTAS = None
+PREFIX_IMPL = 0  # attention kernel of the shared-prompt phase when it runs beside the per-row phase (0 = dgpt_fmha_prefill's choice)
 SIDE_PRIORITY = -1  # stream of the shared-prompt attention phase: ahead of the per-row phase it runs beside
 
 
@@ -263,7 +264,8 @@ class ForwardPlan:
                     prefix_phase = lambda: ops.fmha_prefill(  # noqa: E731
                         self.q, b.shared_layouts[i], self.prefix_o, B=n_seq // N, H=H, Tq=N, D=D,
                         q_batch_stride=N * C, q_row_stride=C, o_batch_stride=N * C, o_row_stride=C,
-                        kv_len=b.shared_len, causal=False, lse=self.prefix_lse, impl=b.fmha_impl, status=self.status,
+                        kv_len=b.shared_len, causal=False, lse=self.prefix_lse,
+                        impl=PREFIX_IMPL if (self.side is not None and PREFIX_IMPL) else b.fmha_impl, status=self.status,
                         max_ctas=self.prefix_ctas if self.side is not None else 0,
                     )
                     po, pl = self.prefix_o, self.prefix_lse
