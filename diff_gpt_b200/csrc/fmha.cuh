@@ -50,5 +50,7 @@ int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st);
 // the same with two query tiles per CTA taking turns on the tensor cores (fmha_pp.cu); `tp` and the maps come from fmha_tc
 struct TcMaps;
 int fmha_tc_pp_launch(const FmhaArgs& a, const TcMaps& maps, TcParams p, long long kv_span, cudaStream_t st);
+// the persistent warp-specialised kernel with one query tile per work item (fmha_ws.cu)
+int fmha_tc_ws_launch(const FmhaArgs& a, const TcMaps& maps, TcParams p, long long kv_span, cudaStream_t st);
 
 }  // namespace dgpt

@@ -42,6 +42,7 @@
 // out stores its site in the status word, raises the CTA-wide abort flag so that the other roles stop waiting too,
 // the loader drains the copies it issued, and the CTA frees its TMEM and returns.
 #include "fmha.cuh"
+#include "fmha_sched.cuh"
 #include "tcgen05.cuh"
 
 namespace dgpt {
@@ -51,35 +52,6 @@ constexpr int kPpThreads = 384;  // three warpgroups: softmax of tile 0, softmax
 constexpr int kPpSoftmaxRegs = 216, kPpHelperRegs = 72;  // registers per thread after the warpgroups trade them
 
 constexpr uint32_t kPpTmemCols = 512;
-
-// Which item a CTA works on next.  Groups of `group_bh` (batch, head) pairs; inside a group the items (pair of
-// query tiles x (batch, head)) are ordered longest first and dealt to the CTAs round by round, every other round
-// in reverse, so that each CTA gets about the same number of key tiles.
-struct PpSched {
-  int n_cta, cta, n_pairs, BH, group_bh, causal;
-  int group = 0, round = 0;
-  __device__ bool next(int& bh, int& pair) {
-    for (;;) {
-      const int first = group * group_bh;
-      if (first >= BH) return false;
-      const int members = min(group_bh, BH - first);
-      const int count = members * n_pairs;
-      const int base = round * n_cta;
-      if (base >= count) {
-        ++group;
-        round = 0;
-        continue;
-      }
-      const int pos = base + ((round & 1) ? (n_cta - 1 - cta) : cta);
-      ++round;
-      if (pos >= count) continue;
-      const int rank = pos / members;
-      bh = first + pos - rank * members;
-      pair = causal ? n_pairs - 1 - rank : rank;
-      return true;
-    }
-  }
-};
 
 struct PpItem {
   int b, h, q0, klen;
@@ -150,10 +122,10 @@ fmha_tc_pp_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
-  PpSched sched;
+  ItemSched sched;
   sched.n_cta = (int)gridDim.x;
   sched.cta = (int)blockIdx.x;
-  sched.n_pairs = (p.Tq + 2 * kBM - 1) / (2 * kBM);
+  sched.n_units = (p.Tq + 2 * kBM - 1) / (2 * kBM);
   sched.BH = p.BH;
   sched.group_bh = p.group_bh;
   sched.causal = p.causal;
@@ -505,12 +477,7 @@ int fmha_tc_pp_launch(const FmhaArgs& a, const TcMaps& maps, TcParams p, long lo
   const int D = a.D == 32 ? 64 : a.D;  // head_dim 32 rides on the 64-wide kernel (zero-filled boxes)
   const int n_pairs = (a.Tq + 2 * kBM - 1) / (2 * kBM);
   p.BH = a.B * a.H;
-  // (batch, head) pairs worked on together: their K and V (2 x span x D bf16 each) should stay in L2 (about 48 MB of it)
-  const long long per_bh = 2ll * kv_span * D * 2;
-  long long group = per_bh > 0 ? (48ll << 20) / per_bh : p.BH;
-  if (group < 1) group = 1;
-  if (group > p.BH) group = p.BH;
-  p.group_bh = (int)group;
+  p.group_bh = sched_group_bh(kv_span, D, p.BH);
   int sms = 0, dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

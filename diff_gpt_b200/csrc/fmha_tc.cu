@@ -1,25 +1,11 @@
 // tcgen05 / TMEM attention for bf16, head_dim 64 or 128 (sm_100a): causal / chunk prefill, and the
 // shared-prompt phase of the Monte-Carlo decode (all trajectories of a series against the prompt K/V).
 //
-// fmha_tc_ws_kernel (impl = 2 of dgpt_fmha_prefill, chosen from 4096 keys on): one CTA of 320 threads per
-// 128-query tile of one (batch, head), one CTA per SM, all 512 TMEM columns.  The warps have fixed roles:
-//   warp 9, lane 0  loader: TMA loads of Q (once) and of the K / V tiles (128-byte swizzle, one box per
-//                   page and per 64-wide half of D) into a ring of 3 K slots and 2 V slots
-//   warp 8, lane 0  issuer: S_j = Q K_j^T into one of two S buffers in TMEM, and O += P_j V_j with P read
-//                   from TMEM (A operand) and V MN-major; it issues P V for tile j, then S for tile j + 2,
-//                   so the tensor cores work on one tile while the softmax warps work on the next
-//   warps 0-7       softmax, two threads per query row: warp w owns the TMEM lanes of quarter w & 3 and the
-//                   key columns of half w >> 2.  A thread reads its 64 scores with tcgen05.ld, swaps its
-//                   partial maximum with the row's other thread through an 8-byte shared-memory word
-//                   (value + turn number, polled with the same clock limit as every wait), writes P as
-//                   packed bf16 into one of two P buffers (tcgen05.st) and rescales its half of O in TMEM
-//                   only when the maximum has moved by more than 2^8.  Two warps per scheduler keep the
-//                   exp2 unit fed while the other instructions of the tile issue (with one thread per row
-//                   a tile took about 1680 cycles of softmax against 1024 of MMA).
-// TMEM columns: S0 [0,128)  S1 [128,256)  P0 [256,320)  P1 [320,384)  O [384, 384 + D).
-// mbarriers: Q loaded; K slot full x3 / free x3; V slot full x2; S ready x2; P ready x2 (256 arrivals);
-// P V done x2 (frees the P buffer and the V slot).  The K-free barriers are separate from
-// S-ready so that the loader can never run two phases ahead of a barrier it waits on.
+// Three kernels share the tensor maps and parameters built here:
+//   fmha_tc_ws_kernel (fmha_ws.cu, impl = 2 of dgpt_fmha_prefill, chosen from 4096 keys on): persistent, warp-specialised,
+//                     one query tile per work item, scores double-buffered in TMEM
+//   fmha_tc_pp_kernel (fmha_pp.cu, impl = 4): persistent, two query tiles per work item
+//   fmha_tc_kernel    (below, impl = 3): the small one
 //
 // fmha_tc_kernel (impl = 3 of dgpt_fmha_prefill; the earlier, simpler form): 128 threads, no
 // fixed roles, 256 TMEM columns and two CTAs per SM so that one CTA's softmax overlaps the other's MMAs.
@@ -316,402 +302,6 @@ fmha_tc_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ C
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
 }
 
-// ---- warp-specialised variant ------------------------------------------------------------------
-// 256 softmax threads (two per query row), one warp whose first lane issues every tcgen05.mma and one warp
-// whose first lane issues every TMA load.  Scores and probabilities are double-buffered in TMEM (S0, S1 at
-// columns 0 and 128; P0, P1 as packed bf16 at 256 and 320; O at 384), K tiles live in a ring of three, V tiles
-// in a ring of two, and all hand-offs are mbarriers:
-//   bar_s[b]  S of a tile is in buffer b                     (tcgen05.commit)
-//   bar_p[b]  all 256 softmax threads have written P into b  (256 thread arrivals)
-//   bar_o[b]  the P V product of that tile is done            (tcgen05.commit)
-// so the softmax of tile j overlaps P V of tile j-1 and Q K^T of tile j+1.  One CTA per SM (512 TMEM columns).
-constexpr int kWsThreads = 320;  // 8 softmax warps, the MMA issuer's warp, the loader's warp
-constexpr uint32_t kWsTmemCols = 512;
-
-template <int D>
-__global__ void __launch_bounds__(kWsThreads, 1)
-fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
-                  const __grid_constant__ CUtensorMap mv, const TcParams p) {
-  constexpr int kSub = D / 64;
-  constexpr uint32_t kSubBytes = kBN * 128;
-  constexpr uint32_t kTileBytes = kSub * kSubBytes;
-  constexpr uint32_t kIdescS = instr_desc(kBN, false);
-  constexpr uint32_t kIdescPV = instr_desc(D, true);
-  constexpr uint32_t kPCol = 256;  // P buffer b: columns [256 + 64 b, +64)
-  constexpr uint32_t kOCol = 384;
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sV = smem + 4 * kTileBytes;  // Q | K0 K1 K2 | V0 V1   (K is needed a tile earlier than V: deeper ring)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  // [2 turns][2 halves][128 rows] words of (turn number + 1) << 32 | value: what the two threads of a row exchange
-  volatile unsigned long long* xch = reinterpret_cast<volatile unsigned long long*>(bars + 32);
-  const uint32_t aQ = smem_u32(smem), aK = aQ + kTileBytes, aV = aQ + 4 * kTileBytes;
-  const uint32_t bar_q = smem_u32(bars);
-  const uint32_t bar_k0 = bar_q + 8, bar_v0 = bar_q + 32, bar_s0 = bar_q + 48, bar_p0 = bar_q + 64, bar_o0 = bar_q + 80,
-                 bar_kf0 = bar_q + 96;  // K slot released (its S product has been computed)
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int pt = p.page_tokens;
-  auto init_barriers = [&](bool again) {  // thread 0; `again`: every phase of the previous work item has completed
-    if (again)
-      for (int i = 0; i < 15; ++i) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar_q + 8 * i) : "memory");
-    mbar_init(bar_q, 1);
-    mbar_init(bar_k0 + 16, 1);
-    for (int i = 0; i < 3; ++i) mbar_init(bar_kf0 + 8 * i, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bar_k0 + 8 * i, 1);
-      mbar_init(bar_v0 + 8 * i, 1);
-      mbar_init(bar_s0 + 8 * i, 1);
-      mbar_init(bar_p0 + 8 * i, 2 * kBM);
-      mbar_init(bar_o0 + 8 * i, 1);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    fence_async_smem();
-  };
-  if (tid == 0) {
-    *abort_flag = 0;
-    init_barriers(false);
-  }
-  if (tid < 2 * kBM) {  // turn numbers of a previous CTA on this SM must not be mistaken for this one's
-    xch[tid] = 0ull;
-    xch[2 * kBM + tid] = 0ull;
-  }
-  if (warp == 0) {
-    tmem_alloc(smem_u32(tmem_slot), kWsTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-
-  // A CTA takes the work items (query tile, head, batch) cta, cta + n_cta, ...: one each when the grid covers them
-  // all; a smaller grid (max_ctas) keeps the kernel on part of the GPU.  Barriers and hand-over words start every
-  // item afresh, so the per-item code below can derive every phase from the tile index.
-  const int n_cta = (int)(gridDim.x * gridDim.y * gridDim.z);
-  const int cta = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
-  for (int work = cta; work < p.n_work; work += n_cta) {
-  if (work != cta) {
-    tc_fence_before();
-    __syncthreads();
-    if (*abort_flag) break;  // a wait ran out in the previous item: the roles have drained, leave together
-    if (tid == 0) init_barriers(true);
-    if (tid < 2 * kBM) {
-      xch[tid] = 0ull;
-      xch[2 * kBM + tid] = 0ull;
-    }
-    __syncthreads();
-    tc_fence_after();
-  }
-  const int qt_idx = work % p.n_qt, bh = work / p.n_qt;
-  const int h = bh % p.H, b = bh / p.H;
-  const int qt = p.causal ? p.n_qt - 1 - qt_idx : qt_idx;  // long tiles first
-  const int q0 = qt * kBM;
-  const int klen = p.kv_len ? p.kv_len[b] : p.kv_len_all;
-  const int kmax = p.causal ? min(klen, p.q_offset + min(q0 + kBM, p.Tq)) : klen;
-  const int n_tiles = kmax > 0 ? (kmax + kBN - 1) / kBN : 0;
-  bool fail = false;
-
-  if (warp == 9) {
-    // ================= loader: every TMA load (one lane) =================
-    if ((tid & 31) == 0 && n_tiles > 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&mq)) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&mk)) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&mv)) : "memory");
-      auto load_kv = [&](const CUtensorMap* map, uint32_t dst, uint32_t bar, int j) {
-        const int t0 = j * kBN;
-        if (pt >= kBN) {
-          const int lp = t0 / pt, in = t0 - lp * pt;
-          const int pg = p.page_table ? p.page_table[(long long)b * p.max_pages + lp] : b;
-          mbar_expect_tx(bar, kTileBytes);
-#pragma unroll
-          for (int s = 0; s < kSub; ++s) tma_load_4d(dst + s * kSubBytes, map, bar, s * 64, in, h, pg);
-        } else {
-          const int per = kBN / pt;
-          int valid = 0;
-          for (int q = 0; q < per; ++q) valid += (t0 + q * pt < klen) ? 1 : 0;
-          mbar_expect_tx(bar, (uint32_t)valid * pt * 128u * kSub);
-          for (int q = 0; q < valid; ++q) {
-            const int lp = t0 / pt + q;
-            const int pg = p.page_table ? p.page_table[(long long)b * p.max_pages + lp] : b;
-#pragma unroll
-            for (int s = 0; s < kSub; ++s) tma_load_4d(dst + s * kSubBytes + q * pt * 128, map, bar, s * 64, 0, h, pg);
-          }
-        }
-      };
-      int last_k[3] = {-1, -1, -1}, last_v[2] = {-1, -1};  // parity of the newest load per ring slot (for the drain on failure)
-      mbar_expect_tx(bar_q, kTileBytes);
-#pragma unroll
-      for (int s = 0; s < kSub; ++s) tma_load_4d(aQ + s * kSubBytes, &mq, bar_q, s * 64, h, q0, b);
-      for (int i = 0; i < 3 && i < n_tiles; ++i) {
-        load_kv(&mk, aK + i * kTileBytes, bar_k0 + 8 * i, i);
-        last_k[i] = 0;
-        if (i < 2) {
-          load_kv(&mv, aV + i * kTileBytes, bar_v0 + 8 * i, i);
-          last_v[i] = 0;
-        }
-      }
-      bool ok = true;
-      for (int j = 0; ok && j + 2 < n_tiles; ++j) {  // refill the rings behind the consumers
-        const int buf = j & 1;
-        const uint32_t ph = (uint32_t)((j >> 1) & 1);
-        if (j + 3 < n_tiles) {
-          // K slot j % 3 is free for tile j+3 once S_j has been computed.  The loader may run far behind the
-          // issuer, so it waits on a barrier of its own that completes once per use of the slot (bar_s could
-          // complete twice before the loader looks, which a parity wait cannot tell from "not yet").
-          const int ks = j % 3;
-          ok = wait_or_abort(bar_kf0 + 8 * ks, (uint32_t)((j / 3) & 1), abort_flag, 16);
-          if (!ok) break;
-          load_kv(&mk, aK + ks * kTileBytes, bar_k0 + 8 * ks, j + 3);
-          last_k[ks] = ((j + 3) / 3) & 1;
-        }
-        ok = wait_or_abort(bar_o0 + 8 * buf, ph, abort_flag, 17);  // P_j V_j is done: V slot j % 2 is free for tile j+2
-        if (!ok) break;
-        load_kv(&mv, aV + buf * kTileBytes, bar_v0 + 8 * buf, j + 2);
-        last_v[buf] = (int)(ph ^ 1u);
-      }
-      if (!ok || *abort_flag) {  // something ran out of time: give the copies still in flight a bounded chance to land
-        if (p.status) atomicExch(p.status, *abort_flag ? *abort_flag : 2);
-        mbar_wait(bar_q, 0);
-        for (int i = 0; i < 3; ++i)
-          if (last_k[i] >= 0) mbar_wait(bar_k0 + 8 * i, (uint32_t)last_k[i]);
-        for (int i = 0; i < 2; ++i)
-          if (last_v[i] >= 0) mbar_wait(bar_v0 + 8 * i, (uint32_t)last_v[i]);
-      }
-    }
-  } else if (warp == 8) {
-    // ================= MMA issuer (one lane) =================
-    if ((tid & 31) == 0 && n_tiles > 0) {
-      constexpr int kStepsS = D / 16, kStepsPV = kBN / 16;
-      // The products are issued as one asm statement each (constant descriptor steps): this lane shares its scheduler
-      // with two softmax warps, and every instruction it does not execute is time the tensor pipe does not wait for.
-      const uint64_t dQK = smem_desc(0, 16, 1024), dV = smem_desc(0, kSubBytes, 1024);
-      auto issue_s = [&](int buf, int kslot) {  // S(buf) = Q K(kslot)^T
-        tc_fence_after();
-        umma_ss_chain<kStepsS>(tmem + buf * 128, dQK + (aQ >> 4), dQK + ((aK + kslot * kTileBytes) >> 4), kIdescS, kSubBytes >> 4);
-        umma_commit(bar_s0 + 8 * buf);
-        umma_commit(bar_kf0 + 8 * kslot);
-      };
-      int last_s[2] = {-1, -1}, last_o[2] = {-1, -1};  // parity of the newest commit per buffer (for the drain on failure)
-      bool ok = wait_or_abort(bar_q, 0, abort_flag, 18);
-      for (int i = 0; ok && i < 2 && i < n_tiles; ++i) {
-        ok = wait_or_abort(bar_k0 + 8 * i, 0, abort_flag, 19);
-        if (ok) {
-          issue_s(i, i);
-          last_s[i] = 0;
-        }
-      }
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        const int buf = j & 1;
-        const uint32_t ph = (uint32_t)((j >> 1) & 1);
-        const bool next_s = j + 2 < n_tiles;
-        // P_j is complete when every row has arrived; by then every row has also consumed S_j, so the same
-        // buffer can take S_{j+2} at once (P lives in its own columns)
-        ok = wait_or_abort(bar_p0 + 8 * buf, ph, abort_flag, 20);
-        ok = ok && wait_or_abort(bar_v0 + 8 * buf, ph, abort_flag, 21);
-        if (ok && next_s) ok = wait_or_abort(bar_k0 + 8 * ((j + 2) % 3), (uint32_t)(((j + 2) / 3) & 1), abort_flag, 22);
-        if (!ok) break;
-        tc_fence_after();
-        umma_ts_chain<kStepsPV>(tmem + kOCol, tmem + kPCol + buf * 64, dV + ((aV + buf * kTileBytes) >> 4), kIdescPV, j > 0 ? 1u : 0u);
-        umma_commit(bar_o0 + 8 * buf);
-        last_o[buf] = (int)ph;
-        if (next_s) {
-          issue_s(buf, (j + 2) % 3);
-          last_s[buf] = (int)(ph ^ 1u);
-        }
-      }
-      if (!ok) {
-        if (!*abort_flag) *abort_flag = 2;
-        if (p.status) atomicExch(p.status, *abort_flag ? *abort_flag : 2);
-        for (int i = 0; i < 2; ++i) {
-          if (last_s[i] >= 0) mbar_wait(bar_s0 + 8 * i, (uint32_t)last_s[i]);
-          if (last_o[i] >= 0) mbar_wait(bar_o0 + 8 * i, (uint32_t)last_o[i]);
-        }
-      }
-    }
-  } else {
-    // ================= softmax threads: two per query row, one for each half of the key tile =================
-    // Warp w works on the TMEM lanes of quarter w & 3 (the only ones it can reach) and on columns
-    // [64 (w >> 2), +64) of S.  The two threads of a row exchange their partial maxima (and, at the end,
-    // their partial sums) through shared memory, handing over with an mbarrier per pair of warps so that
-    // the wait is bounded like every other wait here.
-    constexpr int kHalf = kBN / 2;
-    const int quarter = warp & 3, half = warp >> 2;
-    const int row = quarter * 32 + (tid & 31);
-    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-    float m = -INFINITY, l = 0.f;
-    // Hand-over of one float between the two threads of a row: value and turn number travel in one 8-byte
-    // shared-memory word (a single store, so no fence is needed), slots alternate with the turn's parity,
-    // and the reader polls with a clock-cycle limit like every other wait of this kernel.
-    auto exchange = [&](float mine, int turn, bool& ok) -> float {  // returns the partner's value
-      const int xb = turn & 1;
-      const unsigned long long want = (unsigned long long)(turn + 1) << 32;
-      xch[(xb * 2 + half) * kBM + row] = want | __float_as_uint(mine);
-      const volatile unsigned long long* src = xch + (xb * 2 + (half ^ 1)) * kBM + row;
-      const long long t_begin = clock64();
-      for (int spin = 0;; ++spin) {
-        const unsigned long long got = *src;  // one 8-byte load of what one 8-byte store wrote
-        if ((got >> 32) == (unsigned long long)(turn + 1)) return __uint_as_float((uint32_t)got);
-        if ((spin & 63) == 63 && (*abort_flag || clock64() - t_begin > kWaitLimitCycles)) {
-          if (!*abort_flag) *abort_flag = 27;
-          ok = false;
-          return 0.f;
-        }
-      }
-    };
-    for (int j = 0; j < n_tiles; ++j) {
-      const int buf = j & 1;
-      const uint32_t ph = (uint32_t)((j >> 1) & 1);
-      const int t0 = j * kBN;
-      // exits are taken by whole warps (the vote makes the decision uniform), never by single lanes
-      if (!__all_sync(0xffffffffu, wait_or_abort(bar_s0 + 8 * buf, ph, abort_flag, 23))) {
-        fail = true;
-        break;
-      }
-      tc_fence_after();
-      const int valid_rows = klen - t0;
-      if (valid_rows < kBN) {  // CTA-uniform: last, partial tile
-        if (!__all_sync(0xffffffffu, wait_or_abort(bar_v0 + 8 * buf, ph, abort_flag, 24))) {
-          fail = true;
-          break;
-        }
-        if (half == 0 && row >= valid_rows) {  // value rows past the end may hold anything: clear them so that 0 * x stays 0
-#pragma unroll
-          for (int s = 0; s < kSub; ++s) {
-            uint4* vrow = reinterpret_cast<uint4*>(sV + buf * kTileBytes + s * kSubBytes + row * 128);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
-          }
-          fence_async_smem();
-        }
-      }
-      const bool need_mask = (t0 + kBN > klen) || (p.causal && t0 + kBN - 1 > p.q_offset + q0);
-      const int last_key = p.causal ? min(klen - 1, p.q_offset + q0 + row) : klen - 1;
-      const int c0 = t0 + half * kHalf;  // key index of this thread's first column
-      float sv[kHalf];
-#pragma unroll
-      for (int c = 0; c < kHalf / 32; ++c) tmem_ld32_nowait(lane_addr + buf * 128 + half * kHalf + c * 32, &sv[c * 32]);
-      tc_wait_ld();
-      if (need_mask) {
-#pragma unroll
-        for (int i = 0; i < kHalf; ++i) sv[i] = (c0 + i <= last_key) ? sv[i] : -INFINITY;
-      }
-      float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int i = 0; i < kHalf; i += 8) {  // three-input maxima, four independent chains
-#pragma unroll
-        for (int c = 0; c < 4; ++c) mxs[c] = max3(mxs[c], sv[i + 2 * c], sv[i + 2 * c + 1]);
-      }
-      const float mine = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
-      bool xok = true;
-      const float theirs = exchange(mine, j, xok);
-      if (!__all_sync(0xffffffffu, xok)) {
-        fail = true;
-        break;
-      }
-      const float mx2 = fmaxf(mine, theirs) * p.scale_log2;  // the same number in both threads of the row
-      float alpha = 1.f;  // lazy rescale: the running maximum only moves when exceeded by 2^8
-      if (mx2 > m + 8.f || m == -INFINITY) {
-        alpha = (m == -INFINITY) ? 0.f : ex2(m - mx2);
-        m = mx2;
-      }
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        // O may only be touched when no P V product is in flight: tile j-1's must have finished
-        // (tile j's cannot start before this row has arrived on bar_p below)
-        const bool ok = wait_or_abort(bar_o0 + 8 * (buf ^ 1), (uint32_t)(((j - 1) >> 1) & 1), abort_flag, 25);
-        if (!__all_sync(0xffffffffu, ok)) {
-          fail = true;
-          break;
-        }
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c) {  // this thread's half of the row's O columns
-          float v[32];
-          tmem_ld32(lane_addr + kOCol + half * (D / 2) + c * 32, v);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] *= alpha;
-          tmem_st32(lane_addr + kOCol + half * (D / 2) + c * 32, v);
-        }
-      }
-      const float m_use = (m == -INFINITY) ? 0.f : m;
-      const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
-      uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};  // four packed partial sums (bit pattern of 0.f, 0.f)
-#pragma unroll
-      for (int c = 0; c < kHalf / 32; ++c) {
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float x0, x1;
-          unpack2(fma2(pack2(sv[c * 32 + i], sv[c * 32 + i + 1]), scale2, negm2), x0, x1);  // one issue slot for the pair
-          const float p0 = ex2(x0), p1 = ex2(x1);  // -inf -> 0
-          rs2[(i >> 1) & 3] = add2(rs2[(i >> 1) & 3], pack2(p0, p1));
-          const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
-        }
-        tmem_st16(lane_addr + kPCol + buf * 64 + half * (kHalf / 2) + c * 16, packed);
-      }
-      float ra, rb, rc, rd;
-      unpack2(add2(rs2[0], rs2[1]), ra, rb);
-      unpack2(add2(rs2[2], rs2[3]), rc, rd);
-      l = l * alpha + ((ra + rb) + (rc + rd));  // sum over this thread's columns only
-      tc_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar_p0 + 8 * buf);
-    }
-    // every warp leaves the loop as a whole (waits are on CTA-wide events), so the collective loads below are safe
-    if (!fail && n_tiles > 0) {
-      const int last = n_tiles - 1;
-      if (!wait_or_abort(bar_o0 + 8 * (last & 1), (uint32_t)((last >> 1) & 1), abort_flag, 26)) fail = true;
-      tc_fence_after();
-    }
-    if (!__any_sync(0xffffffffu, fail) && n_tiles > 0) {  // the row's sum is the sum of its two halves
-      bool xok = true;
-      const float theirs = exchange(l, n_tiles, xok);
-      if (xok) l += theirs;
-      else fail = true;
-    }
-    if (!__any_sync(0xffffffffu, fail)) {
-      const int qi = q0 + row;
-      const bool row_ok = qi < p.Tq;
-      const float inv = (l > 0.f && n_tiles > 0) ? 1.f / l : 0.f;
-      const long long off = (long long)b * p.o_bs + (long long)qi * p.o_rs + (long long)h * p.d_head + half * (D / 2);
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        float v[32];
-        if (n_tiles > 0) {
-          tmem_ld32(lane_addr + kOCol + half * (D / 2) + c * 32, v);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0.f;
-        }
-        if (row_ok && half * (D / 2) + c * 32 < p.d_head) {
-          if (p.o_f32) {
-            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.o) + off + c * 32);
-#pragma unroll
-            for (int d = 0; d < 32; d += 4)
-              dst[d >> 2] = make_float4(v[d] * inv, v[d + 1] * inv, v[d + 2] * inv, v[d + 3] * inv);
-          } else {
-            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.o) + off + c * 32;
-#pragma unroll
-            for (int d = 0; d < 32; d += 8) st16<__nv_bfloat16>(dst + d, v + d, inv);
-          }
-        }
-      }
-      if (half == 0 && row_ok && p.lse)
-        p.lse[((long long)b * p.Tq + qi) * p.H + h] = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
-    } else if (p.status) {
-      atomicExch(p.status, *abort_flag ? *abort_flag : 2);
-    }
-  }
-  }  // work items
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, kWsTmemCols);
-}
-
 }  // namespace tc
 
 bool fmha_tc_supported(const FmhaArgs& a, const dgpt_kv_layout& kv) {
@@ -783,22 +373,9 @@ int fmha_tc(const FmhaArgs& a, const dgpt_kv_layout& kv, cudaStream_t st) {
   if (smem < 80 * 1024) smem = 80 * 1024;
   cudaError_t e;
   if (!a.two_cta) {
-    // warp-specialised kernel: Q + two K + two V tiles, padded so that one CTA owns an SM (it allocates all 512 TMEM columns)
-    size_t ws_smem = (size_t)6 * (D / 64) * kBN * 128 + 8192 + 1024;  // tiles, barriers and exchange area, alignment slack
-    if (ws_smem < 120 * 1024) ws_smem = 120 * 1024;
-    const dim3 ws_grid = (a.max_ctas > 0 && a.max_ctas < p.n_work) ? dim3((unsigned)a.max_ctas) : grid;
-    if (D == 64) {
-      e = cudaFuncSetAttribute(fmha_tc_ws_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ws_smem);
-      if (e == cudaSuccess) fmha_tc_ws_kernel<64><<<ws_grid, kWsThreads, ws_smem, st>>>(mq, mk, mv, p);
-    } else {
-      e = cudaFuncSetAttribute(fmha_tc_ws_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ws_smem);
-      if (e == cudaSuccess) fmha_tc_ws_kernel<128><<<ws_grid, kWsThreads, ws_smem, st>>>(mq, mk, mv, p);
-    }
-    if (e != cudaSuccess) {
-      set_error("fmha_tc: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-      return DGPT_E_CUDA;
-    }
-    return launch_status("fmha_tc_ws");
+    const long long span = a.causal ? (long long)a.Tq + a.q_offset
+                                    : (a.kv_len ? (long long)kv.max_pages * kv.page_tokens : (long long)a.kv_len_all);
+    return fmha_tc_ws_launch(a, maps, p, span, st);
   }
   // one CTA per work item, or fewer CTAs that loop over the items when the caller wants the kernel on few SMs
   const unsigned n_cta = (a.max_ctas > 0 && a.max_ctas < p.n_work) ? (unsigned)a.max_ctas : (unsigned)p.n_work;
