@@ -228,15 +228,19 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
     // Hand-over of one float between the two threads of a row: value and turn number travel in one 8-byte
     // shared-memory word (a single store, so no fence is needed), slots alternate with the turn's parity,
     // and the reader polls with a clock-cycle limit like every other wait of this kernel.
-    auto exchange = [&](float mine, bool& ok) -> float {  // returns the partner's value
+    const volatile unsigned long long* partner = nullptr;
+    unsigned long long want = 0ull;
+    auto publish = [&](float mine) {  // this thread's value for the current turn
       const unsigned xb = turn & 1u;
-      const unsigned long long want = (unsigned long long)(turn + 1u) << 32;
+      want = (unsigned long long)(turn + 1u) << 32;
       xch[(xb * 2 + half) * kBM + row] = want | __float_as_uint(mine);
-      const volatile unsigned long long* src = xch + (xb * 2 + (half ^ 1)) * kBM + row;
-      const long long t_begin = clock64();
+      partner = xch + (xb * 2 + (half ^ 1)) * kBM + row;
       ++turn;
+    };
+    auto collect = [&](bool& ok) -> float {  // the partner's value for the turn last published
+      const long long t_begin = clock64();
       for (int spin = 0;; ++spin) {
-        const unsigned long long got = *src;  // one 8-byte load of what one 8-byte store wrote
+        const unsigned long long got = *partner;  // one 8-byte load of what one 8-byte store wrote
         if ((got >> 32) == (want >> 32)) return __uint_as_float((uint32_t)got);
         if ((spin & 63) == 63 && (*abort_flag || clock64() - t_begin > kWaitLimitCycles)) {
           if (!*abort_flag) *abort_flag = 27;
@@ -244,6 +248,10 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           return 0.f;
         }
       }
+    };
+    auto exchange = [&](float mine, bool& ok) -> float {
+      publish(mine);
+      return collect(ok);
     };
     while (!fail && sched.next(bh, qt)) {
       const WsItem it = ws_item(p, bh, qt);
@@ -292,57 +300,80 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           for (int c = 0; c < 4; ++c) mxs[c] = max3(mxs[c], sv[i + 2 * c], sv[i + 2 * c + 1]);
         }
         const float mine = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
-        bool xok = true;
-        const float theirs = exchange(mine, xok);
+        publish(mine);  // the row's other thread will want it; nobody waits for it yet
+        // One sweep turns this thread's 64 scores into probabilities against a reference maximum `ref` (log2 domain),
+        // writes them as packed bf16 into the P buffer and returns their sum.
+        auto sweep = [&](float ref) -> float {
+          const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-ref, -ref);
+          uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};  // four packed partial sums (bit pattern of 0.f, 0.f)
+#pragma unroll
+          for (int c = 0; c < kHalf / 32; ++c) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float x0, x1;
+              unpack2(fma2(pack2(sv[c * 32 + i], sv[c * 32 + i + 1]), scale2, negm2), x0, x1);  // one issue slot for the pair
+              const float p0 = ex2(x0), p1 = ex2(x1);  // -inf -> 0
+              rs2[(i >> 1) & 3] = add2(rs2[(i >> 1) & 3], pack2(p0, p1));
+              const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+              packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
+            }
+            tmem_st16(lane_addr + kPCol + buf * 64 + half * (kHalf / 2) + c * 16, packed);
+          }
+          float ra, rb, rc, rd;
+          unpack2(add2(rs2[0], rs2[1]), ra, rb);
+          unpack2(add2(rs2[2], rs2[3]), rc, rd);
+          return (ra + rb) + (rc + rd);
+        };
+        // From an item's second tile on the running maximum is almost always still good (it only has to be within 2^8
+        // of the true one), so the probabilities are taken against it at once, while the partner's half-maximum is
+        // still on its way; it is read after the sweep, when it has long arrived.  Both threads of a row then hold the
+        // same row maximum and take the same decision: only if it exceeds the running maximum by more than 2^8 is the
+        // tile redone the careful way.  (m is the same in both threads, so the vote below is the same in both warps.)
+        bool xok = true, settled = false;
+        float theirs = 0.f, sum = 0.f;
+        const bool fast = __all_sync(0xffffffffu, m != -INFINITY);
+        if (fast) {
+          sum = sweep(m);
+          theirs = collect(xok);
+        } else {
+          theirs = collect(xok);
+        }
         if (!__all_sync(0xffffffffu, xok)) {
           fail = true;
           break;
         }
         const float mx2 = fmaxf(mine, theirs) * p.scale_log2;  // the same number in both threads of the row
-        float alpha = 1.f;  // lazy rescale: the running maximum only moves when exceeded by 2^8
-        if (mx2 > m + 8.f || m == -INFINITY) {
-          alpha = (m == -INFINITY) ? 0.f : ex2(m - mx2);
-          m = mx2;
+        if (fast && !__any_sync(0xffffffffu, mx2 > m + 8.f)) {
+          l += sum;
+          settled = true;
         }
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-          // O may only be touched when no P V product is in flight: tile g-1's must have finished
-          // (tile g's cannot start before this row has arrived on bar_p below)
-          const bool ok = wait_or_abort(bar_o0 + 8 * (buf ^ 1u), ((g - 1) >> 1) & 1u, abort_flag, 25);
-          if (!__all_sync(0xffffffffu, ok)) {
-            fail = true;
-            break;
+        if (!settled) {
+          float alpha = 1.f;  // lazy rescale: the running maximum only moves when exceeded by 2^8
+          if (mx2 > m + 8.f || m == -INFINITY) {
+            alpha = (m == -INFINITY) ? 0.f : ex2(m - mx2);
+            m = mx2;
           }
-          tc_fence_after();
+          if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+            // O may only be touched when no P V product is in flight: tile g-1's must have finished
+            // (tile g's cannot start before this row has arrived on bar_p below)
+            const bool ok = wait_or_abort(bar_o0 + 8 * (buf ^ 1u), ((g - 1) >> 1) & 1u, abort_flag, 25);
+            if (!__all_sync(0xffffffffu, ok)) {
+              fail = true;
+              break;
+            }
+            tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < D / 64; ++c) {  // this thread's half of the row's O columns
-            float v[32];
-            tmem_ld32(lane_addr + kOCol + half * (D / 2) + c * 32, v);
+            for (int c = 0; c < D / 64; ++c) {  // this thread's half of the row's O columns
+              float v[32];
+              tmem_ld32(lane_addr + kOCol + half * (D / 2) + c * 32, v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= alpha;
-            tmem_st32(lane_addr + kOCol + half * (D / 2) + c * 32, v);
+              for (int i = 0; i < 32; ++i) v[i] *= alpha;
+              tmem_st32(lane_addr + kOCol + half * (D / 2) + c * 32, v);
+            }
           }
+          l = l * alpha + sweep((m == -INFINITY) ? 0.f : m);  // sum over this thread's columns only
         }
-        const float m_use = (m == -INFINITY) ? 0.f : m;
-        const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-m_use, -m_use);
-        uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};  // four packed partial sums (bit pattern of 0.f, 0.f)
-#pragma unroll
-        for (int c = 0; c < kHalf / 32; ++c) {
-          uint32_t packed[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float x0, x1;
-            unpack2(fma2(pack2(sv[c * 32 + i], sv[c * 32 + i + 1]), scale2, negm2), x0, x1);  // one issue slot for the pair
-            const float p0 = ex2(x0), p1 = ex2(x1);  // -inf -> 0
-            rs2[(i >> 1) & 3] = add2(rs2[(i >> 1) & 3], pack2(p0, p1));
-            const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pk);
-          }
-          tmem_st16(lane_addr + kPCol + buf * 64 + half * (kHalf / 2) + c * 16, packed);
-        }
-        float ra, rb, rc, rd;
-        unpack2(add2(rs2[0], rs2[1]), ra, rb);
-        unpack2(add2(rs2[2], rs2[3]), rc, rd);
-        l = l * alpha + ((ra + rb) + (rc + rd));  // sum over this thread's columns only
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(bar_p0 + 8 * buf);
