@@ -302,7 +302,7 @@ static int decode_launch(const void* q, long long q_stride, const KvView& kv, co
   float* ws_ml = ws ? ws + RH * n_splits * D : nullptr;
   const float scale_log2 = kLog2e / sqrtf((float)D);
   dim3 grid((unsigned)((RH + 3) / 4), (unsigned)n_splits);
-  if (part_lse)  // runs beside the shared-prompt kernel: the lighter form
+  if (part_lse)  // runs beside the shared-prompt kernel: the lighter form (the full form there: 1280 against 1255 ms)
     launch_dep(decode_attn_kernel<T, D, kDecLoads / 2, kDecMinCtas * 2>, grid, dim3(128), 0, st, static_cast<const T*>(q),
                q_stride, kv, len0, start1, len1, step_ptr, prefix_o, prefix_lse, static_cast<const T*>(gate), gate_stride,
                static_cast<T*>(y), y_stride, ws_ml, ws_o, part_o, part_lse, n_splits, R, H, scale_log2);

@@ -107,11 +107,14 @@ class Block(nn.Module):
 CACHE_NORMS = True  # depth mix: reuse the norm factors of committed candidates instead of recomputing them
 FUSED_FFN = True  # first feed-forward GEMM on the library's tcgen05 kernel with the SwiGLU fused (bf16 only)
 FUSED_FFN_MIN_ROWS = 256
-# Cap on the CTAs of the shared-prompt attention phase while it runs beside the per-row phase: None = one per SM
-# (two per SM, the kernel's own residency, leave no registers for the per-row kernel: 1270 against 1250 ms per
-# 255 config-4 steps; caps below ~100 make this phase the longer one), 0 = no cap.
-PREFIX_CTAS = None
-PREFIX_IMPL = 0  # attention kernel of the shared-prompt phase when it runs beside the per-row phase (0 = dgpt_fmha_prefill's choice)
+# The shared-prompt attention phase while it runs beside the per-row phase: which kernel (an `impl` of
+# dgpt_fmha_prefill) and on how many SMs.  Measured per 255 config-4 steps, one process, alternating: the persistent
+# kernel with two query tiles per CTA on 64 SMs, which it owns outright (it fills an SM's shared memory and TMEM)
+# while the HBM-bound per-row kernel has the other 84 to itself, 1249-1259 ms; on 48 or 80 SMs 1256-1262; the small
+# kernel (impl 3) on every SM, one CTA each, sharing the SMs with the per-row kernel, 1271-1275; the persistent kernel
+# with one query tile per CTA on 64 SMs 1267-1271, on 40 SMs 1288 (the phase becomes the longer one).
+PREFIX_CTAS = 64
+PREFIX_IMPL = 4
 SIDE_PRIORITY = -1  # stream of the shared-prompt attention phase: ahead of the per-row phase it runs beside
 
 
@@ -222,9 +225,8 @@ class ForwardPlan:
             self.part_o = torch.empty((self.n, H, D), dtype=torch.float32, device=dev)
             self.part_lse = torch.empty((self.n, H), dtype=torch.float32, device=dev)
             self.side = torch.cuda.Stream(device=dev, priority=SIDE_PRIORITY)
-            self.prefix_ctas = (
-                torch.cuda.get_device_properties(dev).multi_processor_count if PREFIX_CTAS is None else PREFIX_CTAS
-            )
+            n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+            self.prefix_ctas = n_sm if PREFIX_CTAS is None else min(PREFIX_CTAS, n_sm)
         if b.n_splits > 1 and self.workspace is None:
             nbytes = ops.decode_attn_workspace_bytes(self.n, H, D, b.n_splits)
             self.workspace = torch.empty(nbytes // 4, dtype=torch.float32, device=dev)
