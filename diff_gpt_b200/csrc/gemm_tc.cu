@@ -61,7 +61,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
-template <int BN>
+// DRAW selects the fourth epilogue at compile time, so that the three storing epilogues do not carry its registers
+// and branches (with the mode tested at run time the feed-forward GEMM took 21.1 instead of 17.7 us on 2048 rows).
+template <int BN, bool DRAW>
 __global__ void __launch_bounds__(kGThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ CUtensorMap mw, const GemmParams p) {
   constexpr int kGN = BN;
@@ -184,7 +186,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
       int best_n = 0x7fffffff;
       long long traj = 0;
       int step = 0;
-      if (p.mode == 3 && row < p.M) {
+      if (DRAW && row < p.M) {
         traj = p.draw.traj_ids ? p.draw.traj_ids[row] : p.draw.traj_id0 + row;
         step = p.draw.step_base + (p.draw.step_ptr ? *p.draw.step_ptr : 0);
       }
@@ -193,7 +195,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
         float v[32];
         tmem_ld32(lane_addr + a * kAccStride + c, v);  // all lanes load; stores below are predicated
         if (row >= p.M) continue;
-        if (p.mode == 3) {
+        if constexpr (DRAW) {
           using B = Io<__nv_bfloat16>;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {  // four columns per random-number block
@@ -220,6 +222,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
           }
           continue;
         }
+        if (DRAW) continue;
         if (p.mode == 0 || p.mode == 2) {
           __nv_bfloat16* dst = p.out + (long long)row * p.out_rs + col0 + c;
 #pragma unroll
@@ -252,7 +255,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ma, const __grid_constant__ C
           }
         }
       }
-      if (p.mode == 3 && row < p.M && best_n != 0x7fffffff)
+      if (DRAW && row < p.M && best_n != 0x7fffffff)
         atomicMax(p.draw.best + row, ((unsigned long long)float_order_bits(best_v) << 32) | (uint32_t)(~(uint32_t)best_n));
       tc_fence_before();
       mbar_arrive(bar_acce + 8 * a);
@@ -356,9 +359,12 @@ int dgpt::linear_launch(const void* a, int64_t a_row_stride, const void* w, int6
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
     cudaError_t e = cudaSuccess;
     const int big = (int)((size_t)tc::kGStages * (tc::kGABytes + 256 * 128) + 256 + 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::gemm_tc_kernel<192>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::gemm_tc_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::gemm_tc_kernel<192, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::gemm_tc_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::gemm_tc_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::gemm_tc_kernel<192, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc::gemm_tc_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
     if (e != cudaSuccess || n <= 0) {
       set_error("linear: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       return DGPT_E_CUDA;
@@ -392,9 +398,13 @@ int dgpt::linear_launch(const void* a, int64_t a_row_stride, const void* w, int6
   const size_t smem = (size_t)tc::kGStages * (tc::kGABytes + (size_t)bn * 128) + 256 + 1024;
   const int tiles = tiles_m * ((N + bn - 1) / bn);
   const int grid = tiles < n_sm[dev] ? tiles : n_sm[dev];
-  if (bn == 256) launch_dep(tc::gemm_tc_kernel<256>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
-  else if (bn == 192) launch_dep(tc::gemm_tc_kernel<192>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
-  else launch_dep(tc::gemm_tc_kernel<128>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
+  if (epilogue == 3) {
+    if (bn == 256) launch_dep(tc::gemm_tc_kernel<256, true>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
+    else if (bn == 192) launch_dep(tc::gemm_tc_kernel<192, true>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
+    else launch_dep(tc::gemm_tc_kernel<128, true>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
+  } else if (bn == 256) launch_dep(tc::gemm_tc_kernel<256, false>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
+  else if (bn == 192) launch_dep(tc::gemm_tc_kernel<192, false>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
+  else launch_dep(tc::gemm_tc_kernel<128, false>, dim3(grid), dim3(tc::kGThreads), smem, st, ma, mw, p);
   return launch_status("linear");
 }
 
