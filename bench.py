@@ -4,8 +4,9 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 Workload ("step"): W = n_gpus series are decoded per step; each rank prefills the
-1024-token prompt of every series of the step and decodes its contiguous slice of
-4096 / W of that series' 4096 trajectories for 256 tokens with top-p 0.9 /
+1024-token prompt of one series of the step, the ranks exchange the prompt K/V (one
+all-gather), and each decodes its contiguous slice of
+4096 / W of every series' 4096 trajectories for 256 tokens with top-p 0.9 /
 temperature 1 sampling, then the token streams are all-gathered.  Every rank
 therefore carries 4096 trajectories per step whatever N is (weak scaling), and at
 N = 1 a step is exactly one series of config 4.  Model: vocab 4096, n_embd 768,
@@ -346,7 +347,10 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        # a step takes seconds: a collective that has not completed after three minutes never will
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(minutes=3))
     assert TRAJECTORIES % world == 0
     n_local = TRAJECTORIES // world
     series_per_step = world
@@ -370,17 +374,19 @@ def run_ours(args) -> None:
     # of a step: they are built by the first step and reused by the following ones (what a server that
     # decodes one batch after another keeps alive between requests).
     kv_pool = None
-    runs: dict[bool, DecodeRun] = {}
+    runs: dict[tuple, DecodeRun] = {}
 
-    def device_step(step_idx: int, use_graph: bool = not args.no_graph, gather: bool = True):
+    def device_step(step_idx: int, use_graph: bool = not args.no_graph, gather: bool = True, collective: bool = True):
+        """`collective` False: a step that one rank runs alone (the instrumented pass) - it prefills every prompt itself."""
         nonlocal kv_pool
         ids = series_of(step_idx)
         batch = prompts_dev[torch.tensor(ids, device=dev)]
-        run = runs.get(use_graph)
+        run = runs.get((use_graph, collective))
         if run is None:
-            run = runs[use_graph] = DecodeRun(
+            run = runs[(use_graph, collective)] = DecodeRun(
                 model, batch, n_local, HORIZON, sampler, 42, None, traj_offset=rank * n_local, series_offset=ids[0],
                 use_graph=use_graph, kv_pool=kv_pool, overlap_prefix=not args.no_overlap,
+                prefill_group=dist.group.WORLD if (world > 1 and collective) else None,  # one rank prefills a prompt, K/V exchanged
             )
             kv_pool = run.cache.pool
         else:
@@ -439,7 +445,7 @@ def run_ours(args) -> None:
         ids = series_of(i)
         toks, _ = engine.generate_many(
             [prompts[s] for s in ids], n_local, HORIZON, sampler, seed=42, traj_offset=rank * n_local,
-            series_offset=ids[0], overlap_prefix=not args.no_overlap,
+            series_offset=ids[0], overlap_prefix=not args.no_overlap, prefill_group=dist.group.WORLD if world > 1 else None,
         )
         full = gather_trajectories(toks, TRAJECTORIES)
         pinned.copy_(full, non_blocking=False)
@@ -509,7 +515,7 @@ def run_ours(args) -> None:
     if rank == 0 and not args.no_kernel_pass:
         timer = _lib.KernelTimer()
         with _lib.timed(timer):
-            _, run = device_step(args.warmup + args.steps, use_graph=False, gather=False)  # rank 0 alone: no collective
+            _, run = device_step(args.warmup + args.steps, use_graph=False, gather=False, collective=False)  # rank 0 alone
         torch.cuda.synchronize(dev)
         del run
         kernels = {k: {kk: round(vv, 4) if isinstance(vv, float) else vv for kk, vv in v.items()} for k, v in timer.summary().items()}

@@ -104,6 +104,10 @@ def decode_sharded(engine, prompts, num_samples: int, group=None, store=None, st
     from .model.engine import SHARED_PREFIX_MIN_ROWS
 
     kwargs.setdefault("shared_prefix", num_samples >= SHARED_PREFIX_MIN_ROWS)
+    # every rank decodes other trajectories of the same prompts: prefill each prompt on one rank only and exchange the
+    # prompt K/V (needs every rank in the call, so only when none of them is left without trajectories)
+    if world > 1 and num_samples >= world and len(prompts) % world == 0:
+        kwargs.setdefault("prefill_group", group if group is not None else dist.group.WORLD)
     if store is None or world == 1:
         toks, masks = engine.generate_many(prompts, count, traj_offset=first, **kwargs)
     else:

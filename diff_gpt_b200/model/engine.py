@@ -25,6 +25,7 @@ from __future__ import annotations
 from typing import Callable, Generator
 
 import torch
+import torch.distributed as dist
 
 from .. import _lib, ops
 from ..sampler.sampler import Sampler
@@ -50,13 +51,13 @@ class DecodeRun:
 
     @staticmethod
     def key_for(model, prompt_lens, num_samples, max_tokens, sampler, seed, has_force, page_tokens, use_graph,
-                fmha_impl, overlap_prefix, shared_prefix=None, fused_head=True) -> tuple:
+                fmha_impl, overlap_prefix, shared_prefix=None, fused_head=True, prefill_shared=False) -> tuple:
         spec = (1.0, 1.0) if sampler is None else (sampler.native_spec() if isinstance(sampler, Sampler) else None)
         emb = model.token_embedding_table.weight
         return (
             id(model), str(emb.device), emb.dtype, tuple(prompt_lens), num_samples, max_tokens, spec,
             None if spec is not None else id(sampler), seed, has_force, page_tokens, use_graph, fmha_impl,
-            overlap_prefix, shared_prefix, fused_head,
+            overlap_prefix, shared_prefix, fused_head, prefill_shared,
         )
 
     def __init__(
@@ -77,6 +78,7 @@ class DecodeRun:
         overlap_prefix: bool = True,
         shared_prefix: bool | None = None,
         fused_head: bool = True,
+        prefill_group=None,
     ) -> None:
         self.model = model
         emb = model.token_embedding_table.weight
@@ -102,7 +104,7 @@ class DecodeRun:
         self.prompt_lens = lens
         self.key = self.key_for(
             model, lens, N, G, sampler, seed, force_schedules is not None, page_tokens, use_graph, fmha_impl,
-            overlap_prefix, shared_prefix, fused_head,
+            overlap_prefix, shared_prefix, fused_head, prefill_group is not None,
         )
         self.packed = model.packed_weights()  # the graph holds these tensors' addresses
         self.cache = PagedKVCache(L, H, D, S, N, max(lens), G, dt, dev, page_tokens=page_tokens, pool=kv_pool)
@@ -117,11 +119,24 @@ class DecodeRun:
         if force_schedules is not None:
             self.force = torch.zeros((S, G), dtype=torch.int32, device=dev)
 
+        # ---- who prefills which prompt ----
+        # Ranks that decode different trajectories of the SAME series (dist.decode_sharded) all need every prompt's
+        # K/V.  With a process group each rank prefills a contiguous block of S / W series only and the ranks exchange
+        # the prompt pages and the last-position logits with one all-gather each (NCCL; each rank's own memory only).
+        self.prefill_group, self.prefill_world, self.prefill_rank = None, 1, 0
+        if prefill_group is not None and dist.is_available() and dist.is_initialized():
+            w = dist.get_world_size(prefill_group)
+            if w > 1 and S % w == 0:
+                self.prefill_group, self.prefill_world, self.prefill_rank = prefill_group, w, dist.get_rank(prefill_group)
+        per_rank = S // self.prefill_world
+        mine = range(self.prefill_rank * per_rank, (self.prefill_rank + 1) * per_rank)
+
         # ---- prefill plans, one per distinct prompt length; only the last position's logits are needed ----
         self.logits0 = torch.empty((S, model.vocab_size), dtype=dt, device=dev)
         groups: dict[int, list[int]] = {}
         for s, n in enumerate(lens):
-            groups.setdefault(n, []).append(s)
+            if s in mine:
+                groups.setdefault(n, []).append(s)
         zero = torch.zeros(S, dtype=torch.int32, device=dev)
         self.prefills = []
         for P, members in groups.items():
@@ -208,8 +223,28 @@ class DecodeRun:
                 self.logits0.copy_(out)
             else:
                 self.logits0[idx] = out
+        if self.prefill_group is not None:
+            self._exchange_prompts()
         self.done = 0
         self.rng = None
+
+    def _exchange_prompts(self) -> None:
+        """Every rank has prefilled its block of series: all-gather the prompt pages (they are the first pages of the
+        pool, series-major, so a block of series is one run of pages per layer) and the last-position logits."""
+        W, r, S = self.prefill_world, self.prefill_rank, self.S
+        n = (S // W) * self.cache.prefix_pages
+        pool = self.cache.pool
+        if getattr(self, "_stage", None) is None:
+            self._stage = torch.empty((W, pool.shape[0], n) + tuple(pool.shape[2:]), dtype=pool.dtype, device=pool.device)
+            self._stage_logits = torch.empty_like(self.logits0)
+        local = pool[:, r * n : (r + 1) * n].contiguous()
+        dist.all_gather_into_tensor(self._stage.view(-1), local.view(-1), group=self.prefill_group)
+        for other in range(W):
+            if other != r:
+                pool[:, other * n : (other + 1) * n].copy_(self._stage[other])
+        mine = self.logits0[r * (S // W) : (r + 1) * (S // W)].contiguous()
+        dist.all_gather_into_tensor(self._stage_logits.view(-1), mine.view(-1), group=self.prefill_group)
+        self.logits0.copy_(self._stage_logits)
 
     # -- sampling ---------------------------------------------------------------------
     def _sample_first(self) -> None:
@@ -355,6 +390,7 @@ class Engine:
         fmha_impl: int = 0,
         overlap_prefix: bool = True,
         shared_prefix: bool | None = None,
+        prefill_group=None,
     ) -> tuple[torch.Tensor, torch.Tensor]:
         """Decode every prompt `num_samples` times.
 
@@ -367,7 +403,9 @@ class Engine:
         the random stream, so a shard of the trajectories reproduces exactly its part of the full run;
         `shared_prefix` (None = decide from `num_samples`) fixes whether the prompt's keys are read once per series
         by the tensor-core phase or per row, so that a shard can take the path the whole job takes.
-        `num_samples == 0` (a rank without work) returns empty tensors.
+        `num_samples == 0` (a rank without work) returns empty tensors.  `prefill_group`: a process group whose ranks
+        decode different trajectories of these same prompts; each rank then prefills only its share of the prompts
+        and the ranks exchange the prompt K/V (every rank of the group must make the call).
         """
         assert isinstance(self.model, GPT), "generate_many needs the diff_gpt_b200 GPT"
         assert len(prompts) > 0 and all(len(p) > 0 for p in prompts), "tokens must be non-empty"
@@ -389,7 +427,7 @@ class Engine:
         lens = [int(prompts.shape[1])] * S if on_device else [len(p) for p in prompts]
         key = DecodeRun.key_for(
             self.model, lens, num_samples, G, sampler, seed, force_schedules is not None, page_tokens, use_graph,
-            fmha_impl, overlap_prefix, shared_prefix,
+            fmha_impl, overlap_prefix, shared_prefix, True, prefill_group is not None,
         )
         run = self._run
         if run is not None and run.key == key and run.reusable():
@@ -399,7 +437,7 @@ class Engine:
             run = DecodeRun(
                 self.model, prompts, num_samples, G, sampler, seed, force_schedules, traj_offset=traj_offset,
                 series_offset=series_offset, page_tokens=page_tokens, use_graph=use_graph, fmha_impl=fmha_impl,
-                overlap_prefix=overlap_prefix, shared_prefix=shared_prefix,
+                overlap_prefix=overlap_prefix, shared_prefix=shared_prefix, prefill_group=prefill_group,
             )
             self._run = run
         run.start()

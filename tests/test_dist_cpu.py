@@ -83,6 +83,7 @@ class _FakeEngine:
 
     def generate_many(self, prompts, count, traj_offset=0, **kwargs):
         self.calls.append((count, traj_offset, kwargs.get("shared_prefix")))
+        self.prefill_group = kwargs.get("prefill_group")
         if self.fail:
             raise RuntimeError("device-side status 2: a bounded wait ran out")
         t = _fake_tokens(len(prompts), traj_offset, count, 4)
