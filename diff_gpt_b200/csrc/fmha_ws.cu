@@ -205,11 +205,12 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           ok = ok && wait_or_abort(bar_v0 + 8 * buf, ph, abort_flag, 21);
           if (ok && j + 2 < n) ok = wait_or_abort(bar_k0 + 8 * ((g + 2) % 3u), ((g + 2) / 3u) & 1u, abort_flag, 22);
           if (!ok) break;
-          // the scores of tile g + 2 first: the softmax warps will want them while this tile's P V only feeds O
-          if (j + 2 < n) issue_s(g + 2, j + 2 == n - 1);
           tc_fence_after();
           umma_ts_chain<kStepsPV>(tmem + kOCol, tmem + kPCol + buf * 64, dV + ((aV + buf * kTileBytes) >> 4), kIdescPV, j > 0 ? 1u : 0u);
           umma_commit(bar_o0 + 8 * buf);
+          // The scores of tile g + 2 go BEHIND this product: their completion (bar_s) then also says that P_g has been
+          // read, which is what lets the softmax threads overwrite the P buffer without a wait of their own.
+          if (j + 2 < n) issue_s(g + 2, j + 2 == n - 1);
         }
         g0 += (unsigned)n;
       }

@@ -189,6 +189,7 @@ class ForwardPlan:
         self.part_o = None
         self.part_lse = None
         self.side = None
+        self.prefix_on_tc = False
         self.prefix_ctas = 0
         self.workspace = None
 
@@ -227,6 +228,12 @@ class ForwardPlan:
             self.side = torch.cuda.Stream(device=dev, priority=SIDE_PRIORITY)
             n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
             self.prefix_ctas = n_sm if PREFIX_CTAS is None else min(PREFIX_CTAS, n_sm)
+            # the persistent tensor-core kernel covers bf16 heads of 32, 64 or 128 in pages that tile its 128-key
+            # blocks; other models leave the choice to the library (its warp-level kernel)
+            pt = int(b.shared_layouts[0].page_tokens)
+            self.prefix_on_tc = (
+                self.q.dtype == torch.bfloat16 and D in (32, 64, 128) and pt >= 8 and (pt % 128 == 0 or 128 % pt == 0)
+            )
         if b.n_splits > 1 and self.workspace is None:
             nbytes = ops.decode_attn_workspace_bytes(self.n, H, D, b.n_splits)
             self.workspace = torch.empty(nbytes // 4, dtype=torch.float32, device=dev)
@@ -267,7 +274,8 @@ class ForwardPlan:
                         self.q, b.shared_layouts[i], self.prefix_o, B=n_seq // N, H=H, Tq=N, D=D,
                         q_batch_stride=N * C, q_row_stride=C, o_batch_stride=N * C, o_row_stride=C,
                         kv_len=b.shared_len, causal=False, lse=self.prefix_lse,
-                        impl=PREFIX_IMPL if (self.side is not None and PREFIX_IMPL) else b.fmha_impl, status=self.status,
+                        impl=PREFIX_IMPL if (self.side is not None and PREFIX_IMPL and self.prefix_on_tc) else b.fmha_impl,
+                        status=self.status,
                         max_ctas=self.prefix_ctas if self.side is not None else 0,
                     )
                     po, pl = self.prefix_o, self.prefix_lse
