@@ -35,7 +35,11 @@ def _fake_tokens(n_series, first, count, horizon):
 
 def _worker(rank, world, port, n_total, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    except Exception as e:  # the port was taken between choosing it and binding it: the test picks another
+        q.put((rank, repr(e)))
+        return
     try:
         first, count = shard_range(n_total, rank, world)
         local = _fake_tokens(3, first, count, 5)
@@ -55,15 +59,18 @@ def _free_port():
 def test_gathered_result_is_independent_of_world_size():
     for n_total in (8, 7):  # even split and a split that differs by one trajectory
         ctx = mp.get_context("spawn")
-        q = ctx.Queue()
-        port = _free_port()
-        procs = [ctx.Process(target=_worker, args=(r, 2, port, n_total, q)) for r in range(2)]
-        for p in procs:
-            p.start()
-        got = dict(q.get(timeout=120) for _ in range(2))
-        for p in procs:
-            p.join(timeout=60)
-            assert p.exitcode == 0
+        for attempt in range(3):
+            q = ctx.Queue()
+            port = _free_port()
+            procs = [ctx.Process(target=_worker, args=(r, 2, port, n_total, q)) for r in range(2)]
+            for p in procs:
+                p.start()
+            got = dict(q.get(timeout=180) for _ in range(2))
+            for p in procs:
+                p.join(timeout=120)
+                assert p.exitcode == 0, (p.exitcode, got)
+            if not any(isinstance(v, str) for v in got.values()):
+                break
         want = _fake_tokens(3, 0, n_total, 5)
         assert torch.equal(got[0], want) and torch.equal(got[1], want)
 
