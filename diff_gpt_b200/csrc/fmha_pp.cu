@@ -31,7 +31,7 @@
 // the chains of the two tiles interleave, but every change between a product with A in shared memory (Q K^T) and one
 // with A in TMEM (P V) drains the tensor pipe for about 250 cycles, four times per key tile, and a row's 128
 // exponentials keep its thread busy for about 1700 cycles while the exp2 unit is shared with the other tile's warp.
-// The kernel reaches 795 / 880 / 900 TFLOP/s at S = 4096 / 8192 / 16384 against 857 / 974 / 1003 for the kernel with one
+// The kernel reaches 795 / 880 / 900 TFLOP/s at S = 4096 / 8192 / 16384 against 904 / 1010 / 1014 for the kernel with one
 // query tile per CTA and double-buffered scores (fmha_tc_ws_kernel), which therefore stays the default for prefill;
 // this one is selected with impl = 4, and the decode step uses it for the shared-prompt phase, where it owns 64 SMs
 // while the HBM-bound per-row kernel has the others.

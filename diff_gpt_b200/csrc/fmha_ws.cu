@@ -9,10 +9,13 @@
 //                   (A operand) and V MN-major; it issues P V for tile g, then S for tile g + 2, so the tensor cores
 //                   work on one tile while the softmax warps work on the next.  Each product is one asm statement.
 //   warps 0-7       softmax, two threads per query row: warp w owns the TMEM lanes of quarter w & 3 and the key
-//                   columns of half w >> 2.  A thread reads its 64 scores with tcgen05.ld, swaps its partial maximum
-//                   with the row's other thread through an 8-byte shared-memory word (value + turn number, polled
-//                   with the same clock limit as every wait), writes P as packed bf16 into one of two P buffers
-//                   (tcgen05.st) and rescales its half of O in TMEM only when the maximum has moved by more than 2^8.
+//                   columns of half w >> 2.  A thread reads its 64 scores with tcgen05.ld, turns them into
+//                   probabilities against the running maximum in one sweep that also finds the tile's own maximum,
+//                   writes P as packed bf16 into one of two P buffers (tcgen05.st), swaps that maximum with the row's
+//                   other thread through an 8-byte shared-memory word (value + turn number, polled with the same
+//                   clock limit as every wait), and only if the row's maximum has moved by more than 2^8 redoes the
+//                   tile after rescaling its half of O in TMEM.  P V of a tile is issued BEFORE the scores of the
+//                   tile after next, so that the arrival of those scores also says the P buffer has been read.
 // TMEM columns: S0 [0,128)  S1 [128,256)  P0 [256,320)  P1 [320,384)  O [384, 384 + D).
 // mbarriers: Q loaded / Q free; K slot full x3 / free x3; V slot full x2; S ready x2; P ready x2 (256 arrivals);
 // P V done x2 (frees the P buffer and the V slot).  Every barrier completes once per use and each role derives the
@@ -295,19 +298,12 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < kHalf; ++i) sv[i] = (c0 + i <= last_key) ? sv[i] : -INFINITY;
         }
-        float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-        for (int i = 0; i < kHalf; i += 8) {  // three-input maxima, four independent chains
-#pragma unroll
-          for (int c = 0; c < 4; ++c) mxs[c] = max3(mxs[c], sv[i + 2 * c], sv[i + 2 * c + 1]);
-        }
-        const float mine = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
-        publish(mine);  // the row's other thread will want it; nobody waits for it yet
         // One sweep turns this thread's 64 scores into probabilities against a reference maximum `ref` (log2 domain),
         // writes them as packed bf16 into the P buffer and returns their sum.
-        auto sweep = [&](float ref) -> float {
+        auto sweep = [&](float ref, float& top) -> float {
           const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negm2 = pack2(-ref, -ref);
           uint64_t rs2[4] = {0ull, 0ull, 0ull, 0ull};  // four packed partial sums (bit pattern of 0.f, 0.f)
+          float tops[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // the largest exponent met, four chains
 #pragma unroll
           for (int c = 0; c < kHalf / 32; ++c) {
             uint32_t packed[16];
@@ -315,6 +311,7 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
             for (int i = 0; i < 32; i += 2) {
               float x0, x1;
               unpack2(fma2(pack2(sv[c * 32 + i], sv[c * 32 + i + 1]), scale2, negm2), x0, x1);  // one issue slot for the pair
+              tops[(i >> 1) & 3] = max3(tops[(i >> 1) & 3], x0, x1);
               const float p0 = ex2(x0), p1 = ex2(x1);  // -inf -> 0
               rs2[(i >> 1) & 3] = add2(rs2[(i >> 1) & 3], pack2(p0, p1));
               const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
@@ -325,27 +322,36 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
           float ra, rb, rc, rd;
           unpack2(add2(rs2[0], rs2[1]), ra, rb);
           unpack2(add2(rs2[2], rs2[3]), rc, rd);
+          top = fmaxf(fmaxf(tops[0], tops[1]), fmaxf(tops[2], tops[3]));
           return (ra + rb) + (rc + rd);
         };
         // From an item's second tile on the running maximum is almost always still good (it only has to be within 2^8
-        // of the true one), so the probabilities are taken against it at once, while the partner's half-maximum is
-        // still on its way; it is read after the sweep, when it has long arrived.  Both threads of a row then hold the
+        // of the true one), so the probabilities are taken against it at once and the tile's own maximum is found in
+        // the same sweep, as the largest exponent met; the two threads of a row swap theirs afterwards and so hold the
         // same row maximum and take the same decision: only if it exceeds the running maximum by more than 2^8 is the
         // tile redone the careful way.  (m is the same in both threads, so the vote below is the same in both warps.)
         bool xok = true, settled = false;
-        float theirs = 0.f, sum = 0.f;
+        float mx2, sum = 0.f, top;
         const bool fast = __all_sync(0xffffffffu, m != -INFINITY);
         if (fast) {
-          sum = sweep(m);
-          theirs = collect(xok);
-        } else {
-          theirs = collect(xok);
+          sum = sweep(m, top);
+          const float theirs = exchange(top, xok);
+          mx2 = fmaxf(top, theirs) + m;  // exponents were taken against m
+        } else {  // first tile of an item: the maximum first
+          float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int i = 0; i < kHalf; i += 8) {  // three-input maxima, four independent chains
+#pragma unroll
+            for (int c = 0; c < 4; ++c) mxs[c] = max3(mxs[c], sv[i + 2 * c], sv[i + 2 * c + 1]);
+          }
+          const float mine = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
+          const float theirs = exchange(mine, xok);
+          mx2 = fmaxf(mine, theirs) * p.scale_log2;  // the same number in both threads of the row
         }
         if (!__all_sync(0xffffffffu, xok)) {
           fail = true;
           break;
         }
-        const float mx2 = fmaxf(mine, theirs) * p.scale_log2;  // the same number in both threads of the row
         if (fast && !__any_sync(0xffffffffu, mx2 > m + 8.f)) {
           l += sum;
           settled = true;
@@ -374,7 +380,7 @@ fmha_tc_ws_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant_
               tmem_st32(lane_addr + kOCol + half * (D / 2) + c * 32, v);
             }
           }
-          l = l * alpha + sweep((m == -INFINITY) ? 0.f : m);  // sum over this thread's columns only
+          l = l * alpha + sweep((m == -INFINITY) ? 0.f : m, top);  // sum over this thread's columns only
         }
         tc_wait_st();
         tc_fence_before();
