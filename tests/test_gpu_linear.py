@@ -103,3 +103,41 @@ def test_add_epilogue_in_place_and_narrow_tiles(M, N, K):
     assert err <= 6e-3 * want.abs().max().item()
     ref = torch.addmm(resid.cuda(), a.cuda(), w.cuda().t())  # cuBLAS: same single rounding, other summation order
     assert (other.float() - ref.float()).abs().max().item() <= 2e-2 * want.abs().max().item()
+
+
+@pytest.mark.parametrize("mode", ["plain", "swiglu", "add"])
+def test_every_output_within_one_bf16_step_of_the_exact_product_and_repeats_bit_for_bit(mode):
+    """The decode step's shape (4096 x 768 -> 3072, 384 tiles over 148 persistent CTAs, two accumulators in turn): every
+    element against the fp64 product of the same bf16 operands, with a bound of one bf16 rounding step of the value
+    plus the fp32 accumulation error, and five more launches that must reproduce the first bit for bit - an epilogue
+    that reads an accumulator a tile late or early shows up as a few wrong elements in one launch out of several."""
+    from diff_gpt_b200 import ops
+
+    M, N, K = 4096, 3072, 768
+    a, w = _operands(M, N, K, 99)
+    a, w = a.cuda(), w.cuda()
+    resid = torch.randn((M, N), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5)).bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def run():
+        if mode == "swiglu":
+            out = torch.full((M, N // 2), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ops.linear(a, w * 8, out, swiglu=(1.702, 7.0), status=status)
+        elif mode == "add":
+            out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ops.linear(a, w, out, add=resid, status=status)
+        else:
+            out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ops.linear(a, w, out, status=status)
+        return out
+
+    first = run()
+    assert status.item() == 0 and torch.isfinite(first).all()
+    if mode != "swiglu":  # (the SwiGLU form is pinned bit for bit to the plain form + the SwiGLU kernel by the test above)
+        want = a.double() @ w.double().T
+        if mode == "add":
+            want = want + resid.double()
+        excess = (first.double() - want).abs() - (2.0**-8 * want.abs() + 1e-4)
+        assert excess.max().item() <= 0.0, excess.argmax().item()
+    for _ in range(5):
+        assert torch.equal(run(), first)
