@@ -809,7 +809,7 @@ def prefill_attention(world: int, rank: int, dev, lengths=(4096, 8192, 16384, 32
                 ev[1].record()
             ops.fmha_prefill(q_rot, lay, y, B=B, H=H, Tq=S, D=D, q_batch_stride=S * C, q_row_stride=C,
                              o_batch_stride=S * C, o_row_stride=C, kv_len_all=S, causal=True,
-                             impl=2, status=status)  # the library's own choice from 4096 keys on, made explicit so that it cannot fall back
+                             impl=2, status=status)  # the library's own choice from 1024 keys on, made explicit so that it cannot fall back
             if timed:
                 ev[2].record()
             torch.mm(y, wp.t(), out=proj)
@@ -956,7 +956,7 @@ def kernel_case(name: str, iters: int = 8) -> None:
         work = R * (2 * C * 2 * own + 3 * C * 2 + C * 4 + H * 4)
         unit, peak = "GB/s", pk["hbm_gbs"]
     elif name in ("fmha", "fmha_long", "fmha_pair"):
-        # config-5 shapes; "fmha" = S 4096 on the two-CTAs-per-SM kernel (the one used below 4096 keys and for the
+        # config-5 shapes; "fmha" = S 4096 on the two-CTAs-per-SM kernel (the one used below 1024 keys and for the
         # shared-prompt phase), "fmha_long" = S 8192 on the warp-specialised one, "fmha_pair" = S 8192 on the kernel
         # with two query tiles per CTA
         B, H, S, D = 8, 16, (4096 if name == "fmha" else 8192), 128

@@ -204,11 +204,12 @@ extern "C" int dgpt_fmha_prefill(const void* q, int64_t q_batch_stride, int64_t 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const KvView view = make_view(kv);
   const bool tc_ok = fmha_tc_supported(a, *kv);
-  // Which tensor-core kernel: the warp-specialised one pays off on long key ranges (measured: ahead from 4096
-  // keys on); below that, and beside the HBM-bound per-row kernel in decode, two smaller CTAs per SM do better.
+  // Which tensor-core kernel: the persistent warp-specialised one from 1024 keys on (measured against the small one on
+  // one to 256 sequences of 1024 to 3584 keys, heads of 32, 64 and 128: 5 to 65 % ahead; level at 512 keys); below
+  // that two smaller CTAs per SM, each done with its item after a few key tiles.
   const long long span = causal ? (long long)Tq + q_offset
                                 : (kv_len ? (long long)kv->max_pages * kv->page_tokens : (long long)kv_len_all);
-  a.two_cta = impl == 3 || (impl == 0 && span < 4096);
+  a.two_cta = impl == 3 || (impl == 0 && span < 1024);
   a.pingpong = impl == 4;
   if (impl >= 2 && !tc_ok) {
     set_error("fmha_prefill: the tensor-core kernel does not cover dtype %d, head_dim %d with this layout", dtype, D);

@@ -2,7 +2,7 @@
 // shared-prompt phase of the Monte-Carlo decode (all trajectories of a series against the prompt K/V).
 //
 // Three kernels share the tensor maps and parameters built here:
-//   fmha_tc_ws_kernel (fmha_ws.cu, impl = 2 of dgpt_fmha_prefill, chosen from 4096 keys on): persistent, warp-specialised,
+//   fmha_tc_ws_kernel (fmha_ws.cu, impl = 2 of dgpt_fmha_prefill, chosen from 1024 keys on): persistent, warp-specialised,
 //                     one query tile per work item, scores double-buffered in TMEM
 //   fmha_tc_pp_kernel (fmha_pp.cu, impl = 4): persistent, two query tiles per work item
 //   fmha_tc_kernel    (below, impl = 3): the small one

@@ -120,7 +120,7 @@ int dgpt_rope_qknorm_kvappend(const void* q, const void* k, const void* v, int64
  * kv: sequence index = b;  kv_len: device int32 [B] or NULL (then kv_len_all is used).
  * impl: 0 = choose (bf16 with D = 64 or 128 runs on the tcgen05 tensor cores, everything else takes
  * the warp-level online-softmax kernel; of the two tensor-core kernels the warp-specialised one is taken
- * from 4096 keys on, the two-CTAs-per-SM one below), 1 = warp-level kernel, 2 = warp-specialised
+ * from 1024 keys on, the two-CTAs-per-SM one below), 1 = warp-level kernel, 2 = warp-specialised
  * tensor-core kernel or fail, 3 = tensor-core kernel with two CTAs per SM or fail, 4 = persistent tensor-core kernel
  * with two query tiles per CTA or fail.
  * max_ctas: 0, or a cap on the CTAs of the two-CTAs-per-SM kernel, which then loop over the query tiles - for a
